@@ -1,0 +1,206 @@
+// asian.cu -- Asian-option Monte Carlo pricer for sm_100a, one path per thread.
+//
+// The model is the reference's pricer (src/ocaml/Asian.ml:32-72): per monitoring
+// step s = s * exp(drift + vol*z), arithmetic-average call payoff, normals from
+// Box-Muller; its counter-hash generator (src/ocaml/Asian.ml:8-27) is replaced by
+// Philox4x32-10 and a geometric-average payoff is priced beside the arithmetic
+// one. Everything a path needs lives in registers: the Philox state, the
+// running price, its logarithm and the two running sums. Nothing is read from
+// memory and only the reduced sums are written, so the kernel is bound by
+// instruction issue and by the special-function unit (ex2, lg2, sqrt, sin, cos:
+// three MUFU operations per path-step), not by HBM.
+//
+// Random stream, identical to the CPU statement of the workload:
+//   counter = (path low word, call index q, path high word, 0), key = (k0, k1);
+//   call q gives four words x -> u = ((x >> 9) + 0.5) * 2^-23  (exact, in (0,1));
+//   (u1,u2) and (u3,u4) give two Box-Muller pairs = the normals of steps 4q..4q+3.
+// The uniform is formed without an integer-to-float conversion: the 23 bits are
+// placed in the mantissa of 1.0f and (1 - 2^-24) is subtracted, which is exact.
+//
+// Two arithmetic flavours of the same path:
+//   PRECISE  every operation rounded separately in the order of the CPU
+//            statement (no FMA contraction), log2f/exp2f/sinf/cosf/sqrtf from
+//            the CUDA math library, with the reference compiler's scalings
+//            (src/ir/bir_lower.c:1757-1811): exp(x) = exp2(x*1.4426950f),
+//            log(x) = log2(x)*0.6931472f, sin/cos(x) = f(x*0.15915494f*6.2831855f);
+//   FAST     MUFU approximations (ex2/lg2/sqrt/sin/cos .approx), the step carried
+//            in base-2 logarithms so drift and vol are pre-scaled by log2(e) and
+//            one FMA forms the exponent.
+// Payoffs are accumulated in double per thread, then warp shuffle -> shared ->
+// per-block partials -> the block that takes the last ticket adds them in index
+// order (no block waits for another).
+#include "common.cuh"
+
+__device__ __forceinline__ float u01(uint32_t x)
+{
+    return __fadd_rn(__uint_as_float(0x3F800000u | (x >> 9)), -0.99999994f);
+}
+
+__device__ __forceinline__ float mufu_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float mufu_lg2(float x) { float y; asm("lg2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float mufu_sqrt(float x) { float y; asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float mufu_sin(float x) { float y; asm("sin.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ float mufu_cos(float x) { float y; asm("cos.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+
+struct Payoff { float arith, geom; };
+
+template <bool PRECISE>
+__device__ __forceinline__ Payoff asian_path(unsigned long long p, uint32_t k0, uint32_t k1,
+                                             float s0, float strike, float drift, float vol, int nstep)
+{
+    const uint32_t plo = (uint32_t)p, phi = (uint32_t)(p >> 32);
+    const int ncall = nstep >> 2;
+    float s = s0, ls = 0.0f, sum_s = 0.0f, sum_l = 0.0f;
+    Payoff out;
+    if (PRECISE) {
+        for (int q = 0; q < ncall; q++) {
+            const Philox4 r = philox4x32_10(plo, (uint32_t)q, phi, 0u, k0, k1);
+            const float u1 = u01(r.x), u2 = u01(r.y), u3 = u01(r.z), u4 = u01(r.w);
+            const float ra = __fsqrt_rn(__fmul_rn(-2.0f, __fmul_rn(log2f(u1), 0.6931472f)));
+            const float rb = __fsqrt_rn(__fmul_rn(-2.0f, __fmul_rn(log2f(u3), 0.6931472f)));
+            const float ta = __fmul_rn(__fmul_rn(__fmul_rn(6.2831855f, u2), 0.15915494f), 6.2831855f);
+            const float tb = __fmul_rn(__fmul_rn(__fmul_rn(6.2831855f, u4), 0.15915494f), 6.2831855f);
+            float z[4];
+            z[0] = __fmul_rn(ra, cosf(ta)); z[1] = __fmul_rn(ra, sinf(ta));
+            z[2] = __fmul_rn(rb, cosf(tb)); z[3] = __fmul_rn(rb, sinf(tb));
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x = __fadd_rn(drift, __fmul_rn(vol, z[i]));
+                s = __fmul_rn(s, exp2f(__fmul_rn(x, 1.4426950f)));
+                ls = __fadd_rn(ls, x);
+                sum_s = __fadd_rn(sum_s, s);
+                sum_l = __fadd_rn(sum_l, ls);
+            }
+        }
+        const float fn = (float)nstep;
+        const float am = __fsub_rn(__fdiv_rn(sum_s, fn), strike);
+        const float gm = __fsub_rn(__fmul_rn(s0, exp2f(__fmul_rn(__fdiv_rn(sum_l, fn), 1.4426950f))), strike);
+        out.arith = am > 0.0f ? am : 0.0f;
+        out.geom = gm > 0.0f ? gm : 0.0f;
+    } else {
+        const float d2 = drift * 1.4426950f, v2 = vol * 1.4426950f;    // step in log2 units
+        const float c_r = -2.0f * 0.6931472f;                          // -2 ln u = c_r * log2 u
+        for (int q = 0; q < ncall; q++) {
+            const Philox4 r = philox4x32_10(plo, (uint32_t)q, phi, 0u, k0, k1);
+            const float u1 = u01(r.x), u2 = u01(r.y), u3 = u01(r.z), u4 = u01(r.w);
+            const float ra = mufu_sqrt(c_r * mufu_lg2(u1));
+            const float rb = mufu_sqrt(c_r * mufu_lg2(u3));
+            const float ta = 6.2831855f * u2, tb = 6.2831855f * u4;
+            float z[4];
+            z[0] = ra * mufu_cos(ta); z[1] = ra * mufu_sin(ta);
+            z[2] = rb * mufu_cos(tb); z[3] = rb * mufu_sin(tb);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                const float x2 = fmaf(v2, z[i], d2);
+                s *= mufu_ex2(x2);
+                ls += x2;
+                sum_s += s;
+                sum_l += ls;
+            }
+        }
+        const float inv_n = 1.0f / (float)nstep;
+        const float am = sum_s * inv_n - strike;
+        const float gm = s0 * mufu_ex2(sum_l * inv_n) - strike;
+        out.arith = am > 0.0f ? am : 0.0f;
+        out.geom = gm > 0.0f ? gm : 0.0f;
+    }
+    return out;
+}
+
+__device__ __forceinline__ double warp_sum_d(double v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+// out[0..3] = sum arith, sum geom, sum arith^2, sum geom^2 over paths
+// [path0, path0+npaths). Launch with a 1-D grid of 1-D blocks whose size is a
+// multiple of 32. partials needs 4 doubles per block, ticket starts at zero.
+template <bool PRECISE>
+__device__ __forceinline__ void asian_mc_body(double *out, unsigned long long path0,
+                                              unsigned long long npaths, uint32_t k0, uint32_t k1,
+                                              float s0, float strike, float drift, float vol,
+                                              int nstep, double *partials, unsigned *ticket)
+{
+    __shared__ double sh[4][32];
+    __shared__ unsigned s_last;
+    double a1 = 0.0, g1 = 0.0, a2 = 0.0, g2 = 0.0;
+    const unsigned long long T = (unsigned long long)gridDim.x * blockDim.x;
+    for (unsigned long long i = (unsigned long long)blockIdx.x * blockDim.x + threadIdx.x; i < npaths; i += T) {
+        const Payoff pf = asian_path<PRECISE>(path0 + i, k0, k1, s0, strike, drift, vol, nstep);
+        const double a = (double)pf.arith, g = (double)pf.geom;
+        a1 += a; g1 += g; a2 += a * a; g2 += g * g;
+    }
+    const unsigned lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nwarp = blockDim.x >> 5;
+    a1 = warp_sum_d(a1); g1 = warp_sum_d(g1); a2 = warp_sum_d(a2); g2 = warp_sum_d(g2);
+    if (lane == 0) { sh[0][wid] = a1; sh[1][wid] = g1; sh[2][wid] = a2; sh[3][wid] = g2; }
+    __syncthreads();
+    if (wid == 0) {
+        double v[4];
+#pragma unroll
+        for (int k = 0; k < 4; k++) v[k] = warp_sum_d(lane < nwarp ? sh[k][lane] : 0.0);
+        if (lane == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; k++) partials[4 * blockIdx.x + k] = v[k];
+            __threadfence();
+            s_last = (atomicAdd(ticket, 1u) == gridDim.x - 1);
+        }
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // Last block: 4 warps take one of the four sums each and add the block
+    // partials in index order (lane-strided, then the butterfly).
+    if (wid < 4) {
+        double v = 0.0;
+        for (unsigned b = lane; b < gridDim.x; b += 32) v += __ldcg(partials + 4 * b + wid);
+        v = warp_sum_d(v);
+        if (lane == 0) out[wid] = v;
+    }
+    if (threadIdx.x == 0) *ticket = 0u;
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+asian_mc(double *out, unsigned long long path0, unsigned long long npaths, uint32_t k0, uint32_t k1,
+         float s0, float strike, float drift, float vol, int nstep, double *partials, unsigned *ticket)
+{
+    asian_mc_body<false>(out, path0, npaths, k0, k1, s0, strike, drift, vol, nstep, partials, ticket);
+}
+
+extern "C" __global__ void __launch_bounds__(256)
+asian_mc_precise(double *out, unsigned long long path0, unsigned long long npaths, uint32_t k0, uint32_t k1,
+                 float s0, float strike, float drift, float vol, int nstep, double *partials, unsigned *ticket)
+{
+    asian_mc_body<true>(out, path0, npaths, k0, k1, s0, strike, drift, vol, nstep, partials, ticket);
+}
+
+// Per-path payoffs with the parameter list of the CPU statement of the kernel:
+// arith[t], geom[t] for path path0 + t, one thread per path (any 1-D launch;
+// threads beyond npaths do nothing).
+template <bool PRECISE>
+__device__ __forceinline__ void asian_paths_body(float *arith, float *geom, long long path0, long long npaths,
+                                                 uint32_t k0, uint32_t k1, float s0, float strike,
+                                                 float drift, float vol, int nstep)
+{
+    const long long T = (long long)gridDim.x * blockDim.x;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < npaths; t += T) {
+        const Payoff pf = asian_path<PRECISE>((unsigned long long)(path0 + t), k0, k1, s0, strike, drift, vol, nstep);
+        arith[t] = pf.arith;
+        geom[t] = pf.geom;
+    }
+}
+
+extern "C" __global__ void asian_paths(float *arith, float *geom, long long path0, long long npaths,
+                                       uint32_t k0, uint32_t k1, float s0, float strike,
+                                       float drift, float vol, int nstep)
+{
+    asian_paths_body<false>(arith, geom, path0, npaths, k0, k1, s0, strike, drift, vol, nstep);
+}
+
+extern "C" __global__ void asian_paths_precise(float *arith, float *geom, long long path0, long long npaths,
+                                               uint32_t k0, uint32_t k1, float s0, float strike,
+                                               float drift, float vol, int nstep)
+{
+    asian_paths_body<true>(arith, geom, path0, npaths, k0, k1, s0, strike, drift, vol, nstep);
+}

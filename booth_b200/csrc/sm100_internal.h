@@ -1,0 +1,107 @@
+/* sm100_internal.h -- private state shared by the C files of libbooth_sm100. */
+#ifndef SM100_INTERNAL_H
+#define SM100_INTERNAL_H
+
+#include <cuda.h>          /* types and enums only; every entry point is dlsym'ed */
+#include "booth_sm100.h"
+
+/* The driver entry points the library uses, by their exported (versioned)
+ * names. Kept as one table so a missing symbol is reported by name. */
+typedef struct sm100_api {
+    void *lib;
+    CUresult (*Init)(unsigned);
+    CUresult (*DeviceGetCount)(int *);
+    CUresult (*DeviceGet)(CUdevice *, int);
+    CUresult (*DeviceGetName)(char *, int, CUdevice);
+    CUresult (*DeviceGetAttribute)(int *, CUdevice_attribute, CUdevice);
+    CUresult (*PrimaryCtxRetain)(CUcontext *, CUdevice);
+    CUresult (*PrimaryCtxRelease)(CUdevice);
+    CUresult (*CtxSetCurrent)(CUcontext);
+    CUresult (*CtxGetCurrent)(CUcontext *);
+    CUresult (*ModuleLoadData)(CUmodule *, const void *);
+    CUresult (*ModuleUnload)(CUmodule);
+    CUresult (*ModuleGetFunction)(CUfunction *, CUmodule, const char *);
+    CUresult (*FuncGetAttribute)(int *, CUfunction_attribute, CUfunction);
+    CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int);
+    CUresult (*FuncGetParamInfo)(CUfunction, size_t, size_t *, size_t *);   /* optional */
+    CUresult (*MemAlloc)(CUdeviceptr *, size_t);
+    CUresult (*MemFree)(CUdeviceptr);
+    CUresult (*MemcpyHtoD)(CUdeviceptr, const void *, size_t);
+    CUresult (*MemcpyDtoH)(void *, CUdeviceptr, size_t);
+    CUresult (*MemcpyHtoDAsync)(CUdeviceptr, const void *, size_t, CUstream);
+    CUresult (*MemcpyDtoHAsync)(void *, CUdeviceptr, size_t, CUstream);
+    CUresult (*MemsetD8Async)(CUdeviceptr, unsigned char, size_t, CUstream);
+    CUresult (*MemHostAlloc)(void **, size_t, unsigned);
+    CUresult (*MemFreeHost)(void *);
+    CUresult (*StreamCreate)(CUstream *, unsigned);
+    CUresult (*StreamDestroy)(CUstream);
+    CUresult (*StreamSynchronize)(CUstream);
+    CUresult (*EventCreate)(CUevent *, unsigned);
+    CUresult (*EventDestroy)(CUevent);
+    CUresult (*EventRecord)(CUevent, CUstream);
+    CUresult (*EventSynchronize)(CUevent);
+    CUresult (*EventElapsedTime)(float *, CUevent, CUevent);
+    CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned,
+                             unsigned, unsigned, unsigned, unsigned, CUstream,
+                             void **, void **);
+    CUresult (*GetErrorString)(CUresult, const char **);
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
+                                     void *, const cuuint64_t *, const cuuint64_t *,
+                                     const cuuint32_t *, const cuuint32_t *,
+                                     CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+} sm100_api_t;
+
+#define SM100_TRAK_MAX 64
+
+/* Built-in kernels, resolved once per device from the embedded image. */
+enum {
+    SM100_K_VADD, SM100_K_SAXPY, SM100_K_FILL,
+    SM100_K_REDUCE_I32, SM100_K_REDUCE_F32,
+    SM100_K_ASIAN_MC, SM100_K_ASIAN_MC_PRECISE,
+    SM100_K_ASIAN_PATHS, SM100_K_ASIAN_PATHS_PRECISE,
+    SM100_K_GEMM_SPLIT_A, SM100_K_GEMM_SPLIT_BT, SM100_K_GEMM_TF32X3,
+    SM100_K_COUNT
+};
+
+struct sm100_dev {
+    const sm100_api_t *api;
+    int         ordinal;
+    CUdevice    cudev;
+    CUcontext   ctx;
+    CUstream    stream;
+    CUevent     ev0, ev1;
+    CUmodule    image;                 /* built-in kernel image */
+    CUfunction  k[SM100_K_COUNT];
+    char        name[128];
+    int         sm_major, sm_minor, sm_count;
+    unsigned long long launches;
+    char        err[256];
+    /* Scratch owned by the device: block partials and the arrival counter of
+     * the reductions and the pricer. */
+    CUdeviceptr scratch;
+    size_t      scratch_bytes;
+    /* GEMM workspace: the hi/lo planes of A and of B transposed. */
+    CUdeviceptr gemm_ws;
+    size_t      gemm_ws_bytes;
+    /* bc_trak labels. */
+    struct { unsigned long long ptr, size; char label[24]; int flags; } trak[SM100_TRAK_MAX];
+    int         ntrak;
+};
+
+/* Records and prints "sm100_rt: <what>: <driver text>"; returns SM100_ERR_CUDA. */
+int  sm100_fail(sm100_dev_t *dev, const char *what, CUresult rc);
+/* Makes the device's context current on the calling thread. */
+int  sm100_enter(sm100_dev_t *dev);
+/* Launch one of the built-in kernels on the device's stream. */
+int  sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
+                    unsigned shmem, void **args);
+/* Grows the device-owned scratch / GEMM workspace; returns 0 on failure. */
+CUdeviceptr sm100_scratch(sm100_dev_t *dev, size_t bytes);
+CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes);
+
+/* The embedded sm_100a kernel image (image.S). */
+extern const unsigned char booth_sm100_image[];
+extern const unsigned char booth_sm100_image_end[];
+
+#endif

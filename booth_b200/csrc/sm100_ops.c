@@ -1,0 +1,328 @@
+/* sm100_ops.c -- the five workloads, launched with geometry tuned for a B200.
+ *
+ * Each function enqueues work on the device's stream and returns; results stay
+ * in device memory (sm100_rt_sync / sm100_rt_d2h fetch them). The kernels come
+ * from the image embedded in the library. There is no host-side arithmetic on
+ * the data anywhere in this file, and no fallback: a failed launch is reported.
+ *
+ * The CPU-launcher symbols at the end (vector_add, matmul, matmul_k, saxpy) have
+ * the signatures the reference's x86-64 objects export
+ * (examples/cpu_launch_vadd.c:23-24, examples/cpu_launch_matmul.c:22-26); they
+ * take host pointers, stage them through the GPU and copy the result back. */
+#define _POSIX_C_SOURCE 200809L
+#include <limits.h>
+#include <pthread.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "sm100_internal.h"
+
+static int env_int(const char *name, int dflt, int lo, int hi)
+{
+    const char *e = getenv(name);
+    if (!e || !*e) return dflt;
+    int v = atoi(e);
+    if (v < lo) v = lo;
+    if (v > hi) v = hi;
+    return v;
+}
+
+static int bad_arg(sm100_dev_t *dev, const char *what)
+{
+    if (dev) snprintf(dev->err, sizeof dev->err, "%s", what);
+    fprintf(stderr, "sm100_rt: %s\n", what);
+    return SM100_ERR_ARG;
+}
+
+/* Scratch layout: the arrival counter in the first 256 bytes, partials after. */
+#define SCRATCH_TICKET   0
+#define SCRATCH_PARTIALS 256
+
+/* Streaming kernels: 256-thread blocks, each block iteration covers
+ * 256 threads x 4 x 16 bytes; the grid is a multiple of the SM count so every
+ * SM carries the same number of resident blocks, capped by the work there is. */
+static unsigned stream_grid(sm100_dev_t *dev, long long n, unsigned block, unsigned unroll)
+{
+    const int bpsm = env_int("BOOTH_SM100_STREAM_BPSM", 8, 1, 64);
+    long long tiles = ((n >> 2) + (long long)block * unroll - 1) / ((long long)block * unroll);
+    long long g = (long long)dev->sm_count * bpsm;
+    if (tiles < g) g = tiles;
+    if (g < 1) g = 1;
+    return (unsigned)g;
+}
+
+int booth_sm100_fill(sm100_dev_t *dev, sm100_ptr_t dst, long long first, long long n,
+                     uint32_t seed, uint32_t stream, int kind)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (n < 0 || first < 0 || kind < 0 || kind > 2) return bad_arg(dev, "booth_sm100_fill: bad argument");
+    if (n == 0) return SM100_OK;
+    long long nblk = ((first + n + 3) >> 2) - (first >> 2);
+    long long g = (nblk + 255) / 256;
+    if (g > (long long)dev->sm_count * 16) g = (long long)dev->sm_count * 16;
+    void *args[] = { &dst, &first, &n, &seed, &stream, &kind };
+    return sm100_launch_k(dev, SM100_K_FILL, (unsigned)g, 256, 0, args);
+}
+
+int booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y, sm100_ptr_t out, long long n)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (n < 0 || n > INT_MAX) return bad_arg(dev, "booth_sm100_vadd: n must be in [0, 2^31)");
+    if (n == 0) return SM100_OK;
+    int ni = (int)n, bs = 256;
+    const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 256, 32, 1024);
+    void *args[] = { &x, &y, &out, &ni, &bs };
+    return sm100_launch_k(dev, SM100_K_VADD, stream_grid(dev, n, block, 4), block, 0, args);
+}
+
+int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, long long n)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (n < 0 || n > INT_MAX) return bad_arg(dev, "booth_sm100_saxpy: n must be in [0, 2^31)");
+    if (n == 0) return SM100_OK;
+    int ni = (int)n;
+    const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 256, 32, 1024);
+    void *args[] = { &y, &x, &a, &ni };
+    return sm100_launch_k(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 4), block, 0, args);
+}
+
+static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long n, sm100_ptr_t out)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (n < 0 || !out || (in & 3)) return bad_arg(dev, "booth_sm100_reduce: bad argument");
+    const unsigned block = (unsigned)env_int("BOOTH_SM100_REDUCE_BLOCK", 256, 32, 1024) & ~31u;
+    const int bpsm = env_int("BOOTH_SM100_REDUCE_BPSM", 4, 1, 32);
+    long long tiles = ((n >> 2) + (long long)block * 8 - 1) / ((long long)block * 8);
+    long long g = (long long)dev->sm_count * bpsm;
+    if (tiles < g) g = tiles;
+    if (g < 1) g = 1;
+    CUdeviceptr sc = sm100_scratch(dev, SCRATCH_PARTIALS + (size_t)g * 8);
+    if (!sc) return SM100_ERR_ARG;
+    CUdeviceptr partials = sc + SCRATCH_PARTIALS, ticket = sc + SCRATCH_TICKET;
+    void *args[] = { &in, &n, &partials, &ticket, &out };
+    return sm100_launch_k(dev, which, (unsigned)g, block, 0, args);
+}
+
+int booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
+{
+    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out);
+}
+
+int booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
+{
+    return reduce_common(dev, SM100_K_REDUCE_F32, in, n, out);
+}
+
+int booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
+                      long long npaths, sm100_ptr_t out)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (!p || !out || npaths < 0 || path0 < 0 || p->nstep <= 0 || (p->nstep & 3))
+        return bad_arg(dev, "booth_sm100_asian: bad argument (nstep must be a positive multiple of 4)");
+    const unsigned block = 256;
+    const int bpsm = env_int("BOOTH_SM100_ASIAN_BPSM", 4, 1, 8);
+    long long g = (npaths + block - 1) / block;
+    if (g > (long long)dev->sm_count * bpsm) g = (long long)dev->sm_count * bpsm;
+    if (g < 1) g = 1;
+    CUdeviceptr sc = sm100_scratch(dev, SCRATCH_PARTIALS + (size_t)g * 32);
+    if (!sc) return SM100_ERR_ARG;
+    CUdeviceptr partials = sc + SCRATCH_PARTIALS, ticket = sc + SCRATCH_TICKET;
+    unsigned long long p0 = (unsigned long long)path0, np = (unsigned long long)npaths;
+    booth_asian_t q = *p;
+    void *args[] = { &out, &p0, &np, &q.k0, &q.k1, &q.s0, &q.strike, &q.drift, &q.vol,
+                     &q.nstep, &partials, &ticket };
+    return sm100_launch_k(dev, p->precise ? SM100_K_ASIAN_MC_PRECISE : SM100_K_ASIAN_MC,
+                          (unsigned)g, block, 0, args);
+}
+
+int booth_sm100_asian_paths(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
+                            long long npaths, sm100_ptr_t arith, sm100_ptr_t geom)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (!p || !arith || !geom || npaths < 0 || path0 < 0 || p->nstep <= 0 || (p->nstep & 3))
+        return bad_arg(dev, "booth_sm100_asian_paths: bad argument");
+    if (npaths == 0) return SM100_OK;
+    long long g = (npaths + 255) / 256;
+    if (g > (long long)dev->sm_count * 8) g = (long long)dev->sm_count * 8;
+    booth_asian_t q = *p;
+    void *args[] = { &arith, &geom, &path0, &npaths, &q.k0, &q.k1, &q.s0, &q.strike,
+                     &q.drift, &q.vol, &q.nstep };
+    return sm100_launch_k(dev, p->precise ? SM100_K_ASIAN_PATHS_PRECISE : SM100_K_ASIAN_PATHS,
+                          (unsigned)g, 256, 0, args);
+}
+
+/* ---- host-side generator: the same stream as the fill_philox kernel ---- */
+
+static void philox_block(uint32_t c[4], uint32_t k0, uint32_t k1)
+{
+    for (int r = 0; r < 10; r++) {
+        uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
+        uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
+        uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0;
+        uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+        c[0] = n0; c[1] = (uint32_t)p1; c[2] = n2; c[3] = (uint32_t)p0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+}
+
+typedef struct { uint32_t *dst; long long first, lo, hi; uint32_t seed, stream; int kind; } fill_job_t;
+
+static void *fill_worker(void *arg)
+{
+    fill_job_t *j = (fill_job_t *)arg;
+    long long i = j->lo;
+    while (i < j->hi) {
+        long long e = j->first + i;
+        unsigned long long ctr = (unsigned long long)(e >> 2);
+        uint32_t c[4] = { (uint32_t)ctr, (uint32_t)(ctr >> 32), 0, 0 };
+        philox_block(c, j->seed, j->stream);
+        for (int l = (int)(e & 3); l < 4 && i < j->hi; l++, i++) {
+            uint32_t x = c[l], v;
+            if (j->kind == BOOTH_FILL_I32_1000) {
+                v = (uint32_t)((int)(x % 2001u) - 1000);
+            } else {
+                float u = (float)(x >> 8) * 5.9604644775390625e-8f;
+                float f = j->kind == BOOTH_FILL_F32_PM1 ? 2.0f * u - 1.0f : u;
+                memcpy(&v, &f, 4);
+            }
+            j->dst[i] = v;
+        }
+    }
+    return NULL;
+}
+
+void booth_sm100_fill_host(void *dst, long long first, long long n, uint32_t seed,
+                           uint32_t stream, int kind, int threads)
+{
+    if (!dst || n <= 0) return;
+    if (threads < 1) threads = 1;
+    if (threads > 64) threads = 64;
+    if (n < (1 << 16)) threads = 1;
+    pthread_t tid[64];
+    fill_job_t job[64];
+    for (int t = 0; t < threads; t++) {
+        job[t].dst = (uint32_t *)dst; job[t].first = first;
+        job[t].lo = n * t / threads; job[t].hi = n * (t + 1) / threads;
+        job[t].seed = seed; job[t].stream = stream; job[t].kind = kind;
+    }
+    for (int t = 1; t < threads; t++) pthread_create(&tid[t], NULL, fill_worker, &job[t]);
+    fill_worker(&job[0]);
+    for (int t = 1; t < threads; t++) pthread_join(tid[t], NULL);
+}
+
+/* ---- CPU-launcher symbols ---- */
+
+static sm100_dev_t *g_host_dev;
+static pthread_mutex_t g_host_mu = PTHREAD_MUTEX_INITIALIZER;
+
+static void host_die(const char *what)
+{
+    fprintf(stderr, "sm100_rt: %s failed on the GPU path; there is no CPU fallback\n", what);
+    abort();
+}
+
+static sm100_dev_t *host_dev(const char *what)
+{
+    pthread_mutex_lock(&g_host_mu);
+    if (!g_host_dev && sm100_rt_init(&g_host_dev, -1) != SM100_OK) {
+        pthread_mutex_unlock(&g_host_mu);
+        host_die(what);
+    }
+    pthread_mutex_unlock(&g_host_mu);
+    return g_host_dev;
+}
+
+void vector_add(float *x, float *y, float *out, int n_elements, int block_size, int nthreads)
+{
+    /* One call of the CPU launcher covers element indices [0, nthreads): the
+     * kernel's masks are dropped there (src/triton/lower.c:713-760), n_elements
+     * is not consulted. */
+    (void)n_elements; (void)block_size;
+    if (nthreads <= 0) return;
+    sm100_dev_t *d = host_dev("vector_add");
+    size_t bytes = (size_t)nthreads * sizeof(float);
+    sm100_ptr_t dx = sm100_rt_alloc(d, bytes), dy = sm100_rt_alloc(d, bytes), dz = sm100_rt_alloc(d, bytes);
+    if (!dx || !dy || !dz) host_die("vector_add (alloc)");
+    if (sm100_rt_h2d(d, dx, x, bytes) || sm100_rt_h2d(d, dy, y, bytes) ||
+        booth_sm100_vadd(d, dx, dy, dz, nthreads) || sm100_rt_d2h(d, out, dz, bytes))
+        host_die("vector_add");
+    sm100_rt_free(d, dx); sm100_rt_free(d, dy); sm100_rt_free(d, dz);
+}
+
+void saxpy(float *y, float *x, float a, int n, int nthreads)
+{
+    /* tests/canonical.cu:168-173: threads with idx >= n do nothing. */
+    long long m = nthreads < n ? nthreads : n;
+    if (m <= 0) return;
+    sm100_dev_t *d = host_dev("saxpy");
+    size_t bytes = (size_t)m * sizeof(float);
+    sm100_ptr_t dx = sm100_rt_alloc(d, bytes), dy = sm100_rt_alloc(d, bytes);
+    if (!dx || !dy) host_die("saxpy (alloc)");
+    if (sm100_rt_h2d(d, dx, x, bytes) || sm100_rt_h2d(d, dy, y, bytes) ||
+        booth_sm100_saxpy(d, dy, dx, a, m) || sm100_rt_d2h(d, y, dy, bytes))
+        host_die("saxpy");
+    sm100_rt_free(d, dx); sm100_rt_free(d, dy);
+}
+
+/* Extent, in floats, of a strided 4 x K (or K x 4) operand starting at its base. */
+static size_t span(int r, int sr, int c, int sc)
+{
+    long long m = (long long)(r - 1) * (sr > 0 ? sr : 0) + (long long)(c - 1) * (sc > 0 ? sc : 0) + 1;
+    return (size_t)m;
+}
+
+static void tile_matmul(const char *what, float *a, float *b, float *c, int K, int block_k,
+                        int sam, int sak, int sbk, int sbn, int scm, int scn, int accumulate,
+                        int nthreads)
+{
+    if (nthreads <= 0) return;
+    if (sam < 0 || sak < 0 || sbk < 0 || sbn < 0 || scm < 0 || scn < 0 || K <= 0) {
+        fprintf(stderr, "sm100_rt: %s: negative strides are not supported\n", what);
+        abort();
+    }
+    sm100_dev_t *d = host_dev(what);
+    size_t na = span(4, sam, K, sak), nb = span(K, sbk, 4, sbn), nc = span(4, scm, 4, scn);
+    sm100_ptr_t da = sm100_rt_alloc(d, na * 4), db = sm100_rt_alloc(d, nb * 4), dc = sm100_rt_alloc(d, nc * 4);
+    if (!da || !db || !dc) host_die(what);
+    sm100_kern_t k;
+    if (sm100_rt_load_builtin(d, "matmul_tile", &k)) host_die(what);
+    void *args[] = { &da, &db, &dc, &K, &block_k, &sam, &sak, &sbk, &sbn, &scm, &scn, &accumulate };
+    /* The strided tile of c is written in place: bring the surrounding floats
+     * over first so the copy back leaves them untouched. */
+    if (sm100_rt_h2d(d, da, a, na * 4) || sm100_rt_h2d(d, db, b, nb * 4) ||
+        sm100_rt_h2d(d, dc, c, nc * 4) ||
+        sm100_rt_launch(d, &k, 1, 1, 1, 32, 1, 1, 0, args) ||
+        sm100_rt_d2h(d, c, dc, nc * 4))
+        host_die(what);
+    sm100_rt_free(d, da); sm100_rt_free(d, db); sm100_rt_free(d, dc);
+}
+
+void matmul(float *a, float *b, float *c, int stride_am, int stride_ak, int stride_bk,
+            int stride_bn, int stride_cm, int stride_cn, int nthreads)
+{
+    tile_matmul("matmul", a, b, c, 4, 4, stride_am, stride_ak, stride_bk, stride_bn,
+                stride_cm, stride_cn, 0, nthreads);
+}
+
+void matmul_k(float *a, float *b, float *c, int K, int stride_am, int stride_ak, int stride_bk,
+              int stride_bn, int stride_cm, int stride_cn, int nthreads)
+{
+    tile_matmul("matmul_k", a, b, c, K, 2, stride_am, stride_ak, stride_bk, stride_bn,
+                stride_cm, stride_cn, 1, nthreads);
+}
+
+int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t b, int M, int N, int K)
+{
+    (void)c; (void)a; (void)b; (void)M; (void)N; (void)K;
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    fprintf(stderr, "sm100_rt: gemm_tf32x3 is not in this image\n");
+    return SM100_ERR_KERN;
+}

@@ -1,0 +1,238 @@
+/* booth_sm100.h -- the B200 (sm_100a) execution path behind Booth's launcher.
+ *
+ * Three layers, all plain C ABI (pointers, sizes, integers; no C++ or Python
+ * types), all served by libbooth_sm100.so:
+ *
+ *   1. sm100_rt_*      a thin shim over the CUDA driver API, the sm_100a twin of
+ *                      the reference's nv_rt_* (src/nvidia/nv_rt.h:96-127,
+ *                      src/nvidia/nv_rt.c:69-381). It dlopens libcuda.so.1, uses the
+ *                      device's primary context (so NCCL and any other runtime-API
+ *                      user in the process share it) and loads cubins built by nvcc
+ *                      for sm_100a instead of JIT-compiling PTX.
+ *   2. booth_sm100_*   the five workloads with launch geometry tuned for B200:
+ *                      vector add, saxpy, sum reduction, fp32 GEMM (3xTF32 on
+ *                      tcgen05) and the Asian-option Monte Carlo pricer, plus the
+ *                      seeded input generator they are measured on.
+ *   3. sm100_comm_*    the one collective the path has: an NCCL all-reduce of the
+ *                      reduction / Monte Carlo partial sums.
+ *
+ * bc_runtime.h (same directory) is the reference's own launcher API on top of
+ * layer 1. The CPU-launcher symbols at the end of this file let
+ * examples/cpu_launch_vadd.c and examples/cpu_launch_matmul.c relink unchanged.
+ *
+ * There is no CPU fallback anywhere: without a driver, a B200 or the kernel
+ * image every entry point returns an error code and prints one line that
+ * starts with "sm100_rt:" on stderr. */
+#ifndef BOOTH_SM100_H
+#define BOOTH_SM100_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes: the numbering of src/nvidia/nv_rt.h:19-25, extended ---- */
+#define SM100_OK            0
+#define SM100_ERR_DL       -1   /* libcuda / libnccl could not be opened */
+#define SM100_ERR_SYM      -2   /* an entry point is missing from the library */
+#define SM100_ERR_CUDA     -3   /* a driver call returned an error */
+#define SM100_ERR_NO_GPU   -4   /* no device, or the device is not sm_100 */
+#define SM100_ERR_IO       -5   /* kernel image file unreadable */
+#define SM100_ERR_KERN     -6   /* kernel name not found in the image */
+#define SM100_ERR_ARG      -7   /* invalid argument (size, alignment, NULL) */
+#define SM100_ERR_NCCL     -8   /* an NCCL call returned an error */
+
+typedef struct sm100_dev sm100_dev_t;          /* one GPU: context, stream, kernels */
+typedef unsigned long long sm100_ptr_t;        /* device address (CUdeviceptr) */
+
+/* Kernel handle; replaces nv_kern_t (src/nvidia/nv_rt.h:42-46). */
+typedef struct sm100_kern {
+    void    *mod;            /* CUmodule, NULL when the kernel lives in the built-in image */
+    void    *func;           /* CUfunction */
+    uint32_t param_bytes;    /* size of the kernel's parameter block */
+    uint32_t shared_bytes;   /* static shared memory */
+    uint32_t local_bytes;    /* local memory per thread */
+    uint32_t _pad;
+    char     name[128];
+} sm100_kern_t;
+
+/* ---------------------------------------------------------------------------
+ * Layer 1: driver shim
+ * ------------------------------------------------------------------------- */
+
+/* Replaces nv_rt_init (src/nvidia/nv_rt.c:69-156). ordinal < 0 reads the
+ * environment variable BOOTH_DEVICE (default 0). Retains the primary context,
+ * creates one stream, and loads the built-in sm_100a kernel image. */
+int  sm100_rt_init(sm100_dev_t **out, int ordinal);
+/* Replaces nv_rt_shut (src/nvidia/nv_rt.c:160-170). NULL is a no-op. */
+void sm100_rt_shut(sm100_dev_t *dev);
+/* Number of CUDA devices, or a negative status. */
+int  sm100_rt_device_count(void);
+const char *sm100_rt_name(const sm100_dev_t *dev);
+int  sm100_rt_sm_count(const sm100_dev_t *dev);
+int  sm100_rt_ordinal(const sm100_dev_t *dev);
+/* Text of the last error recorded on this device ("" if none). */
+const char *sm100_rt_errs(const sm100_dev_t *dev);
+
+/* Replaces nv_rt_load (src/nvidia/nv_rt.c:172-248): path names a cubin or
+ * fatbin built for sm_100a. */
+int  sm100_rt_load(sm100_dev_t *dev, const char *path, const char *name,
+                   sm100_kern_t *out);
+/* Same, from the kernel image embedded in the library. */
+int  sm100_rt_load_builtin(sm100_dev_t *dev, const char *name, sm100_kern_t *out);
+/* Replaces nv_rt_unload (src/nvidia/nv_rt.c:252-257). */
+void sm100_rt_unload(sm100_dev_t *dev, sm100_kern_t *kern);
+
+/* Replace nv_rt_alloc / nv_rt_free (src/nvidia/nv_rt.c:261-278); 0 on failure. */
+sm100_ptr_t sm100_rt_alloc(sm100_dev_t *dev, size_t size);
+void        sm100_rt_free(sm100_dev_t *dev, sm100_ptr_t ptr);
+/* Replace nv_rt_h2d / nv_rt_d2h (src/nvidia/nv_rt.c:280-300): synchronous. */
+int  sm100_rt_h2d(sm100_dev_t *dev, sm100_ptr_t dst, const void *src, size_t size);
+int  sm100_rt_d2h(sm100_dev_t *dev, void *dst, sm100_ptr_t src, size_t size);
+/* Asynchronous copies on the device's stream (host memory should be pinned). */
+int  sm100_rt_h2d_async(sm100_dev_t *dev, sm100_ptr_t dst, const void *src, size_t size);
+int  sm100_rt_d2h_async(sm100_dev_t *dev, void *dst, sm100_ptr_t src, size_t size);
+/* Fills size bytes with zero on the device's stream. */
+int  sm100_rt_zero(sm100_dev_t *dev, sm100_ptr_t dst, size_t size);
+
+/* Replaces nv_rt_launch (src/nvidia/nv_rt.c:304-327): args points at one
+ * pointer per kernel parameter. Unlike the reference the launch is only
+ * enqueued on the device's stream; sm100_rt_sync waits. */
+int  sm100_rt_launch(sm100_dev_t *dev, const sm100_kern_t *kern,
+                     uint32_t gx, uint32_t gy, uint32_t gz,
+                     uint32_t bx, uint32_t by, uint32_t bz,
+                     uint32_t shmem, void **args);
+/* Launch with the packed parameter struct bc_dispatch receives
+ * (src/runtime/bc_runtime.c:643-658); args_size beyond the kernel's own
+ * parameter block is dropped, a shorter block is zero-padded. */
+int  sm100_rt_launch_packed(sm100_dev_t *dev, const sm100_kern_t *kern,
+                            uint32_t gx, uint32_t gy, uint32_t gz,
+                            uint32_t bx, uint32_t by, uint32_t bz,
+                            uint32_t shmem, const void *args, uint32_t args_size);
+/* Replaces nv_rt_sync (src/nvidia/nv_rt.c:329-346); waits for the stream. */
+int  sm100_rt_sync(sm100_dev_t *dev);
+
+/* Pinned host memory; replace nv_rt_mmap / nv_rt_mfre (src/nvidia/nv_rt.c:348-381). */
+int  sm100_rt_hostalloc(sm100_dev_t *dev, void **hp, size_t size);
+void sm100_rt_hostfree(sm100_dev_t *dev, void *hp);
+
+/* Device-side timing on the device's stream: tic records an event, toc records
+ * a second one, waits for it and returns the milliseconds between the two. */
+int  sm100_rt_tic(sm100_dev_t *dev);
+int  sm100_rt_toc(sm100_dev_t *dev, float *ms);
+/* Number of kernel launches this device has enqueued since sm100_rt_init. */
+unsigned long long sm100_rt_launches(const sm100_dev_t *dev);
+
+/* ---------------------------------------------------------------------------
+ * Layer 2: workloads (all asynchronous on the device's stream; device pointers)
+ * ------------------------------------------------------------------------- */
+
+/* Seeded inputs. Element i is lane i%4 of Philox4x32-10 with counter
+ * (i/4 low word, i/4 high word, 0, 0) and key (seed, stream):
+ *   kind 0: float  uniform in [-1,1):   2*u - 1,  u = (x >> 8) * 2^-24
+ *   kind 1: float  uniform in [0,1):    u
+ *   kind 2: int32  uniform in [-1000,1000]:  (int)(x % 2001) - 1000
+ * The device and host generators give identical bits. first is the index of
+ * the first element written to dst (dst[0] is element `first`), so a shard can
+ * be generated in place. */
+#define BOOTH_FILL_F32_PM1   0
+#define BOOTH_FILL_F32_01    1
+#define BOOTH_FILL_I32_1000  2
+int  booth_sm100_fill(sm100_dev_t *dev, sm100_ptr_t dst, long long first,
+                      long long n, uint32_t seed, uint32_t stream, int kind);
+void booth_sm100_fill_host(void *dst, long long first, long long n,
+                           uint32_t seed, uint32_t stream, int kind, int threads);
+
+/* out[i] = x[i] + y[i]: tests/tri_vadd.py:6-16, tests/vector_add.cu:4-10. */
+int  booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y,
+                      sm100_ptr_t out, long long n);
+/* y[i] = a*x[i] + y[i], product and sum rounded separately:
+ * tests/canonical.cu:168-173 as compiled by src/cpu/cpu_emit.c:538-542. */
+int  booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x,
+                       float a, long long n);
+/* Sum of n int32 with wrapping arithmetic into *out (one int32 on the device):
+ * the tg_reduce / reduce_sum shape, tests/tg_reduce.cu:4-26,
+ * tests/canonical.cu:59-108. */
+int  booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
+                            sm100_ptr_t out);
+/* Sum of n float into out[0] (double) on the device; fp32 per-thread partial
+ * sums, combined in double. The workload's fp32 answer is (float)out[0]. */
+int  booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
+                            sm100_ptr_t out);
+/* C[M,N] = A[M,K] * B[K,N], row-major fp32, 3xTF32 on the tensor cores:
+ * the tests/tri_matmul_k.py:8-23 / tests/canonical.cu:18-50 contraction.
+ * M % 128 == 0, N % 256 == 0, K % 32 == 0. */
+int  booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a,
+                      sm100_ptr_t b, int M, int N, int K);
+
+/* Asian-option Monte Carlo (src/ocaml/Asian.ml:32-72 with Philox4x32-10 in
+ * place of its counter hash). drift = (r - sigma^2/2)*dt and vol = sigma*sqrt(dt)
+ * are computed in fp32 by the caller; nstep must be a multiple of 4. */
+typedef struct booth_asian {
+    float    s0, strike, drift, vol;
+    int32_t  nstep;
+    uint32_t k0, k1;            /* Philox key */
+    int32_t  precise;           /* 0: MUFU approximations, 1: libm-accurate functions */
+} booth_asian_t;
+/* Prices paths [path0, path0+npaths) and writes four doubles to out on the
+ * device: sum of arithmetic payoffs, sum of geometric payoffs, and the sums of
+ * their squares (undiscounted). */
+int  booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
+                       long long npaths, sm100_ptr_t out);
+/* Per-path payoffs, arith[i] and geom[i] for path path0+i (the oracle kernel's
+ * own output, for per-path comparison). */
+int  booth_sm100_asian_paths(sm100_dev_t *dev, const booth_asian_t *p,
+                             long long path0, long long npaths,
+                             sm100_ptr_t arith, sm100_ptr_t geom);
+
+/* ---------------------------------------------------------------------------
+ * Layer 3: the collective (NCCL over NVLink; libnccl.so.2 is dlopen'ed)
+ * The reference has no counterpart: it drives one device only
+ * (src/nvidia/nv_rt.c:132, src/runtime/bc_runtime.c:234-244).
+ * ------------------------------------------------------------------------- */
+typedef struct sm100_comm sm100_comm_t;
+#define SM100_COMM_ID_BYTES 128
+#define SM100_I32 0
+#define SM100_F32 1
+#define SM100_F64 2
+/* One process per GPU: rank 0 makes an id, the host program hands it to every
+ * rank (any transport), each rank calls init_rank with its own device. */
+int  sm100_comm_unique_id(void *id128);
+int  sm100_comm_init_rank(sm100_comm_t **out, sm100_dev_t *dev, int nranks,
+                          int rank, const void *id128);
+/* One process, ndev GPUs. */
+int  sm100_comm_init_all(sm100_comm_t **out, sm100_dev_t **devs, int ndev);
+/* In-place sum over all ranks of count elements at buf, on the device's stream
+ * (communicator made by init_rank). */
+int  sm100_comm_allreduce_sum(sm100_comm_t *comm, sm100_ptr_t buf, size_t count, int dtype);
+/* The same for a communicator made by init_all: one call per device index,
+ * all of them between group_begin and group_end. */
+int  sm100_comm_allreduce_sum_dev(sm100_comm_t *comm, int index, sm100_ptr_t buf,
+                                  size_t count, int dtype);
+int  sm100_comm_group_begin(void);
+int  sm100_comm_group_end(void);
+void sm100_comm_destroy(sm100_comm_t *comm);
+
+/* ---------------------------------------------------------------------------
+ * CPU-launcher symbols (host pointers; stage to the GPU, launch, copy back)
+ * The signatures are those of examples/cpu_launch_vadd.c:23-24 and
+ * examples/cpu_launch_matmul.c:22-26: the kernel's own parameters followed by
+ * nthreads (src/cpu/cpu_emit.c:386-431). They have no error channel; on failure
+ * they print "sm100_rt: ..." and abort(), they never compute on the CPU.
+ * ------------------------------------------------------------------------- */
+void vector_add(float *x, float *y, float *out, int n_elements, int block_size,
+                int nthreads);
+void matmul(float *a, float *b, float *c, int stride_am, int stride_ak,
+            int stride_bk, int stride_bn, int stride_cm, int stride_cn,
+            int nthreads);
+void matmul_k(float *a, float *b, float *c, int K, int stride_am, int stride_ak,
+              int stride_bk, int stride_bn, int stride_cm, int stride_cn,
+              int nthreads);
+void saxpy(float *y, float *x, float a, int n, int nthreads);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BOOTH_SM100_H */

@@ -16,8 +16,9 @@
  *     expf(x) = exp2f(x*1.4426950f), logf(x) = log2f(x)*0.6931472f,
  *     sinf/cosf(x) = libm(x*0.15915494f*6.2831855f).
  * Counter = (path low word, call index q, path high word, 0); key = (k0, k1).
- * Call q yields four uniforms u = ((x >> 8) + 0.5) * 2^-24 and from them the
- * normals of monitoring steps 4q .. 4q+3. nstep must be a multiple of 4. */
+ * Call q yields four uniforms u = ((x >> 9) + 0.5) * 2^-23, exact in fp32 and
+ * strictly inside (0,1), and from them the normals of monitoring steps
+ * 4q .. 4q+3. nstep must be a multiple of 4. */
 
 __device__ unsigned int mulhi32(unsigned int a, unsigned int b)
 {
@@ -27,7 +28,7 @@ __device__ unsigned int mulhi32(unsigned int a, unsigned int b)
 
 __device__ float u01(unsigned int x)
 {
-    return ((float)(x >> 8) + 0.5f) * 5.9604644775390625e-8f;
+    return ((float)(x >> 9) + 0.5f) * 1.1920928955078125e-7f;
 }
 
 __global__ void asian_paths(float *arith, float *geom, long long path0,

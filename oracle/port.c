@@ -118,7 +118,7 @@ static float bk_logf(float x) { return log2f(x) * 0.6931472f; }
 static float bk_turn(float x) { float t = x * 0.15915494f; return t * 6.2831855f; }
 static float bk_sinf(float x) { return sinf(bk_turn(x)); }
 static float bk_cosf(float x) { return cosf(bk_turn(x)); }
-static float u01(uint32_t x) { return ((float)(x >> 8) + 0.5f) * 5.9604644775390625e-8f; }
+static float u01(uint32_t x) { return ((float)(x >> 9) + 0.5f) * 1.1920928955078125e-7f; }
 
 static void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1)
 {

@@ -1,0 +1,94 @@
+"""GPU parity: the Asian-option Monte Carlo pricer against the CPU checker on the
+same Philox stream. Prices within 1e-5 relative; the geometric price also
+against its closed form."""
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+REL = 1e-5
+DISC = math.exp(-0.05)
+
+
+def closed_form_geometric(s0=100.0, k=100.0, r=0.05, sigma=0.2, T=1.0, n=252):
+    mu = (r - 0.5 * sigma * sigma) * T * (n + 1) / (2.0 * n)
+    var = sigma * sigma * T * (n + 1) * (2 * n + 1) / (6.0 * n * n)
+    sg = math.sqrt(var)
+    d2 = (math.log(s0 / k) + mu) / sg
+    d1 = d2 + sg
+    N = lambda x: 0.5 * (1.0 + math.erf(x / math.sqrt(2.0)))
+    return math.exp(-r * T) * (s0 * math.exp(mu + 0.5 * var) * N(d1) - k * N(d2))
+
+
+def gpu_sums(dev, params, path0, npaths):
+    out = dev.alloc(32)
+    dev.asian(params, path0, npaths, out)
+    v = dev.download(out, 4, np.float64)
+    dev.free(out)
+    return v
+
+
+@pytest.mark.parametrize("precise", [1, 0])
+def test_price_matches_cpu_checker(sm, dev, oracle_lib, precise):
+    npaths = 1 << 18
+    prm = sm.asian_params(precise=precise)
+    s = gpu_sums(dev, prm, 0, npaths)
+    oa, og = oracle_lib.asian(prm, 0, npaths)
+    assert abs(s[0] - oa) <= REL * oa, (s[0] / npaths * DISC, oa / npaths * DISC)
+    assert abs(s[1] - og) <= REL * og, (s[1] / npaths * DISC, og / npaths * DISC)
+
+
+@pytest.mark.parametrize("precise", [1, 0])
+def test_per_path_payoffs(sm, dev, oracle_lib, precise):
+    npaths = 1 << 14
+    prm = sm.asian_params(precise=precise)
+    da, dg = dev.alloc(npaths * 4), dev.alloc(npaths * 4)
+    dev.asian_paths(prm, 123456789, npaths, da, dg)
+    ga, gg = dev.download(da, npaths, np.float32), dev.download(dg, npaths, np.float32)
+    _, _, oa, og = oracle_lib.asian(prm, 123456789, npaths, per_path=True)
+    # A path's payoff is about 100*(relative error of S): transcendental
+    # implementations differ by a few ulp per step, so per path we only ask for
+    # agreement to 2e-3 absolute on a price of order 100; the mean must agree
+    # far more tightly (the 1e-5 test above).
+    assert np.max(np.abs(ga - oa)) < 2e-3 and np.max(np.abs(gg - og)) < 2e-3
+    assert np.count_nonzero((ga > 0) != (oa > 0)) <= 2
+    # the reduced sums are the per-path payoffs added in double
+    s = gpu_sums(dev, prm, 123456789, npaths)
+    assert abs(s[0] - ga.astype(np.float64).sum()) <= 1e-9 * s[0]
+    assert abs(s[1] - gg.astype(np.float64).sum()) <= 1e-9 * s[1]
+    assert abs(s[2] - (ga.astype(np.float64) ** 2).sum()) <= 1e-9 * s[2]
+    dev.free(da); dev.free(dg)
+
+
+def test_disjoint_subsequences_add_up(sm, dev):
+    prm = sm.asian_params()
+    n = 100000
+    whole = gpu_sums(dev, prm, 0, n)
+    parts = sum(gpu_sums(dev, prm, lo, hi - lo) for lo, hi in ((0, 33333), (33333, 70001), (70001, n)))
+    assert np.allclose(whole, parts, rtol=1e-12, atol=0)
+    assert np.all(gpu_sums(dev, prm, 0, 0) == 0)
+
+
+def test_geometric_price_vs_closed_form(sm, dev):
+    npaths = 1 << 22
+    prm = sm.asian_params()
+    s = gpu_sums(dev, prm, 0, npaths)
+    mean = s[1] / npaths
+    var = s[3] / npaths - mean * mean
+    se = DISC * math.sqrt(var / npaths)
+    price = DISC * mean
+    cf = closed_form_geometric()
+    assert abs(cf - 5.5655) < 1e-3
+    assert abs(price - cf) < 4 * se, (price, cf, se)
+    # arithmetic average >= geometric average, path by path, hence in the mean
+    assert s[0] > s[1]
+
+
+def test_path_index_above_2_32(sm, dev, oracle_lib):
+    prm = sm.asian_params(precise=1)
+    p0 = (1 << 32) + 5
+    s = gpu_sums(dev, prm, p0, 4096)
+    oa, og = oracle_lib.asian(prm, p0, 4096)
+    assert abs(s[0] - oa) <= 1e-4 * oa and abs(s[1] - og) <= 1e-4 * og

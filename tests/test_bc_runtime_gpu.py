@@ -1,0 +1,128 @@
+"""GPU: Booth's launcher API (bc_*) served by the sm_100a runtime, driven the way
+examples/launch_saxpy.c drives it, plus its host-detectable failure paths."""
+import ctypes as C
+import os
+import subprocess
+
+import numpy as np
+import pytest
+
+from conftest import ROOT
+
+pytestmark = pytest.mark.gpu
+
+
+class SaxpyArgs(C.Structure):
+    # examples/launch_saxpy.c:71-81: {void *y; void *x; float a; uint32_t n}
+    _fields_ = [("y", C.c_void_p), ("x", C.c_void_p), ("a", C.c_float), ("n", C.c_uint32)]
+
+
+@pytest.fixture()
+def bc(sm):
+    L = sm.lib()
+    d = sm.BcDevice()
+    assert L.bc_device_init(C.byref(d)) == 0
+    yield L, d
+    L.bc_device_shutdown(C.byref(d))
+
+
+def test_launch_saxpy_flow(sm, bc):
+    L, d = bc
+    N, BLOCK = 1024, 256
+    k = sm.BcKernel()
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"saxpy", C.byref(k)) == 0
+    assert k.kernarg_size == 24 and k.kernel_object != 0
+    x = np.arange(N, dtype=np.float32)                       # launch_saxpy.c:54-58
+    y = (N - np.arange(N)).astype(np.float32)
+    want = np.float32(2.5) * x + y
+    dx, dy = L.bc_alloc(C.byref(d), N * 4), L.bc_alloc(C.byref(d), N * 4)
+    assert dx and dy
+    L.bc_trak(C.byref(d), dx, N * 4, b"x", 0)
+    assert L.bc_copy_h2d(C.byref(d), dx, x.ctypes.data, N * 4) == 0
+    assert L.bc_copy_h2d(C.byref(d), dy, y.ctypes.data, N * 4) == 0
+    args = SaxpyArgs(dy, dx, 2.5, N)
+    assert L.bc_dispatch(C.byref(d), C.byref(k), (N + BLOCK - 1) // BLOCK, 1, 1, BLOCK, 1, 1,
+                         C.byref(args), C.sizeof(args)) == 0
+    got = np.empty(N, np.float32)
+    assert L.bc_copy_d2h(C.byref(d), got.ctypes.data, dy, N * 4) == 0
+    assert np.array_equal(got, want)
+    L.bc_free(C.byref(d), dx); L.bc_free(C.byref(d), dy); L.bc_free(C.byref(d), None)
+    L.bc_unload_kernel(C.byref(d), C.byref(k))
+    assert k.kernel_object == 0
+
+
+@pytest.mark.parametrize("grid,block", [((1, 1, 1), (1, 1, 1)), ((0, 0, 0), (0, 0, 0)), ((7, 3, 2), (33, 3, 1)),
+                                        ((40, 1, 1), (256, 1, 1)), ((2, 2, 1), (8, 8, 4))])
+def test_any_launch_geometry_and_oversized_args(sm, bc, oracle_lib, grid, block):
+    L, d = bc
+    n = 10001
+    k = sm.BcKernel()
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"saxpy", C.byref(k)) == 0
+    x = sm.fill_host(n, 3, 0, 0); y = sm.fill_host(n, 3, 1, 0)
+    dx, dy = L.bc_alloc(C.byref(d), n * 4), L.bc_alloc(C.byref(d), n * 4)
+    L.bc_copy_h2d(C.byref(d), dx, x.ctypes.data, n * 4)
+    L.bc_copy_h2d(C.byref(d), dy, y.ctypes.data, n * 4)
+
+    class Padded(C.Structure):          # a caller that appends hidden bytes (src/runtime/lf_gpu_hsa.c:243-255)
+        _fields_ = [("a", SaxpyArgs), ("hidden", C.c_uint8 * 18)]
+    args = Padded(SaxpyArgs(dy, dx, 2.5, n))
+    assert L.bc_dispatch(C.byref(d), C.byref(k), *grid, *block, C.byref(args), C.sizeof(args)) == 0
+    got = np.empty(n, np.float32)
+    L.bc_copy_d2h(C.byref(d), got.ctypes.data, dy, n * 4)
+    assert np.array_equal(got.view(np.uint32), oracle_lib.saxpy(y, x, 2.5).view(np.uint32))
+    L.bc_free(C.byref(d), dx); L.bc_free(C.byref(d), dy)
+    L.bc_unload_kernel(C.byref(d), C.byref(k))
+
+
+def test_host_detectable_failures(sm, bc, tmp_path):
+    L, d = bc
+    k = sm.BcKernel()
+    assert L.bc_load_kernel(C.byref(d), b"/nonexistent/file.cubin", b"saxpy", C.byref(k)) == -6   # BC_RT_ERR_IO
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"no_such_kernel", C.byref(k)) == -7  # ERR_SYMBOL
+    junk = tmp_path / "junk.cubin"
+    junk.write_bytes(b"not a cubin at all")
+    assert L.bc_load_kernel(C.byref(d), str(junk).encode(), b"saxpy", C.byref(k)) == -3            # driver refused
+    assert L.bc_dispatch(C.byref(d), C.byref(k), 1, 1, 1, 1, 1, 1, None, 0) == -7                   # nothing loaded
+    assert L.bc_alloc(C.byref(d), 1 << 50) is None                                                # 1 PiB
+    # the device is still usable afterwards
+    p = L.bc_alloc(C.byref(d), 1024)
+    assert p
+    L.bc_free(C.byref(d), p)
+
+
+def test_vector_add_by_name_through_the_shim(sm, dev, oracle_lib):
+    """sm100_rt_load + pointer-per-argument launch, the nv_rt_launch form."""
+    L = sm.lib()
+    k = sm.Kern()
+    assert L.sm100_rt_load(dev.handle, sm.CUBIN_PATH.encode(), b"vector_add", C.byref(k)) == 0
+    assert k.param_bytes == 32
+    n = 777
+    x = sm.fill_host(n, 8, 0, 0); y = sm.fill_host(n, 8, 1, 0)
+    dx, dy, do = dev.upload(x), dev.upload(y), dev.alloc(n * 4)
+    vals = [C.c_ulonglong(dx), C.c_ulonglong(dy), C.c_ulonglong(do), C.c_int(n), C.c_int(256)]
+    argv = (C.c_void_p * 5)(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+    assert L.sm100_rt_launch(dev.handle, C.byref(k), (n + 255) // 256, 1, 1, 256, 1, 1, 0, argv) == 0
+    dev.sync()
+    assert np.array_equal(dev.download(do, n, np.float32), oracle_lib.vadd(x, y))
+    L.sm100_rt_unload(dev.handle, C.byref(k))
+
+
+EXAMPLES = os.path.join(ROOT, "build", "examples")
+
+
+@pytest.mark.parametrize("prog,needs_cubin,expect", [
+    ("launch_saxpy", True, "PASS: all 1024 elements correct"),
+    ("cpu_launch_vadd", False, "OK: Triton vector_add ran"),
+    ("cpu_launch_matmul", False, "OK: Triton matmul ran"),
+])
+def test_reference_example_programs_relinked(sm, prog, needs_cubin, expect):
+    """The reference's own example sources, compiled unchanged where they lie in
+    the reference tree and linked against libbooth_sm100 by the build step."""
+    exe = os.path.join(EXAMPLES, prog)
+    if not os.path.exists(exe):
+        pytest.skip("build/examples/%s was not built (the reference tree was absent at build time)" % prog)
+    cmd = [exe] + ([sm.CUBIN_PATH] if needs_cubin else [])
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120,
+                         env=dict(os.environ, LD_LIBRARY_PATH=os.path.dirname(sm.LIB_PATH)))
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert expect in res.stdout

@@ -1,0 +1,127 @@
+"""GPU parity: vector add and saxpy through the C ABI against the CPU checker
+(the reference compiler's x86-64 objects when built, else their C restatement).
+Bit-exact, as the reference's own example demands (examples/cpu_launch_vadd.c:37-45)."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from conftest import fill_np
+
+pytestmark = pytest.mark.gpu
+
+SIZES = [1, 3, 4, 5, 255, 256, 257, 1000, 4095, 4096, 4097, (1 << 16) - 1, (1 << 16) + 1, 1 << 20, (1 << 22) + 3]
+
+
+def mismatches(got, want):
+    """Bitwise comparison (so -0.0 vs 0.0 and NaN payloads count)."""
+    return int(np.count_nonzero(got.view(np.uint32) != want.view(np.uint32)))
+
+
+def test_device_generator_matches_host_generator(sm, dev):
+    for kind in (0, 1, 2):
+        for first, n in ((0, 4096), (3, 1001), (2 ** 32 + 6, 5000)):
+            p = dev.alloc(n * 4)
+            dev.fill(p, first, n, 0xB0070002, 3, kind)
+            got = dev.download(p, n, np.int32 if kind == 2 else np.float32)
+            want = sm.fill_host(n, 0xB0070002, 3, kind, first=first)
+            assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), (kind, first, n)
+            assert np.array_equal(want, fill_np(first, n, 0xB0070002, 3, kind))
+            dev.free(p)
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_vadd_bit_exact(sm, dev, oracle_lib, n):
+    x = sm.fill_host(n, 0xB0070000, 0, 0)
+    y = sm.fill_host(n, 0xB0070000, 1, 0)
+    dx, dy, do = dev.upload(x), dev.upload(y), dev.alloc(n * 4)
+    dev.vadd(dx, dy, do, n)
+    got = dev.download(do, n, np.float32)
+    want = oracle_lib.vadd(x, y)
+    assert mismatches(got, want) == 0
+    # inject-must-fail: the comparison has teeth (tests/diff/diff_vadd.c:45-46)
+    bad = got.copy()
+    bad[n // 2] = np.nextafter(bad[n // 2], np.float32(10))
+    assert mismatches(bad, want) == 1
+    for p in (dx, dy, do):
+        dev.free(p)
+
+
+@pytest.mark.parametrize("n", SIZES)
+def test_saxpy_bit_exact_unfused(sm, dev, oracle_lib, n):
+    x = sm.fill_host(n, 0xB0070001, 0, 0)
+    y = sm.fill_host(n, 0xB0070001, 1, 0)
+    dx, dy = dev.upload(x), dev.upload(y)
+    dev.saxpy(dy, dx, 2.5, n)
+    got = dev.download(dy, n, np.float32)
+    want = oracle_lib.saxpy(y, x, 2.5)
+    assert mismatches(got, want) == 0
+    # the fused result differs somewhere on random data, so the test can tell
+    if n >= 4096:
+        fused = (np.float64(2.5) * x.astype(np.float64) + y.astype(np.float64)).astype(np.float32)
+        assert mismatches(fused, want) > 0
+    dev.free(dx); dev.free(dy)
+
+
+def test_unaligned_pointers_take_the_scalar_path(sm, dev, oracle_lib):
+    n = 10007
+    x = sm.fill_host(n + 3, 5, 0, 0)
+    y = sm.fill_host(n + 3, 5, 1, 0)
+    dx, dy, do = dev.upload(x), dev.upload(y), dev.alloc((n + 3) * 4)
+    for off in (1, 2, 3):
+        dev.vadd(dx + 4 * off, dy + 4 * off, do + 4 * off, n)
+        got = dev.download(do + 4 * off, n, np.float32)
+        assert mismatches(got, oracle_lib.vadd(x[off:off + n].copy(), y[off:off + n].copy())) == 0
+        ycopy = dev.upload(y)
+        dev.saxpy(ycopy + 4 * off, dx + 4 * off, 2.5, n)
+        got = dev.download(ycopy + 4 * off, n, np.float32)
+        assert mismatches(got, oracle_lib.saxpy(y[off:off + n].copy(), x[off:off + n].copy(), 2.5)) == 0
+        dev.free(ycopy)
+
+
+def test_reference_fixtures(sm, dev):
+    # examples/cpu_launch_vadd.c:31-45: x=i, y=10i, N=8, exact
+    x = np.arange(8, dtype=np.float32); y = 10 * x
+    dx, dy, do = dev.upload(x), dev.upload(y), dev.alloc(32)
+    dev.vadd(dx, dy, do, 8)
+    assert np.array_equal(dev.download(do, 8, np.float32), x + y)
+    # tests/numeric/manifest.json:9-25: saxpy x=1, y=3, a=2 -> 5.0 at n=256/200/255
+    for n in (256, 200, 255):
+        dxx, dyy = dev.upload(np.ones(n, np.float32)), dev.upload(np.full(n, 3, np.float32))
+        dev.saxpy(dyy, dxx, 2.0, n)
+        assert np.array_equal(dev.download(dyy, n, np.float32), np.full(n, 5, np.float32))
+    # tests/diff/vadd_io.h:12-22 style: signed fractional inputs, N=64
+    i = np.arange(64, dtype=np.float32)
+    a = (i - 32) * np.float32(0.37); b = (i * i) * np.float32(-0.013) + np.float32(1.5)
+    da, db, dc = dev.upload(a), dev.upload(b), dev.alloc(256)
+    dev.vadd(da, db, dc, 64)
+    assert mismatches(dev.download(dc, 64, np.float32), a + b) == 0
+
+
+def test_cpu_launcher_symbols_take_host_pointers(sm, dev, oracle_lib):
+    L = sm.lib()
+    n = 5000
+    x = sm.fill_host(n, 9, 0, 0); y = sm.fill_host(n, 9, 1, 0); out = np.full(n, -1, np.float32)
+    L.vector_add(x.ctypes.data, y.ctypes.data, out.ctypes.data, n, 256, n)
+    assert mismatches(out, oracle_lib.vadd(x, y)) == 0
+    want = oracle_lib.saxpy(y, x, 2.5)
+    L.saxpy(y.ctypes.data, x.ctypes.data, 2.5, n, n)
+    assert mismatches(y, want) == 0
+
+
+def test_full_size_saxpy_windows(sm, dev, oracle_lib):
+    """N = 2^30 (4 GiB per vector): inputs generated in place on the device, the
+    result checked bit for bit on windows at the start, an odd middle offset and
+    the end against the CPU checker run on the same stream positions."""
+    n = 1 << 30
+    dx, dy = dev.alloc(n * 4), dev.alloc(n * 4)
+    dev.fill(dx, 0, n, 0xB0070001, 0, 0)
+    dev.fill(dy, 0, n, 0xB0070001, 1, 0)
+    dev.saxpy(dy, dx, 2.5, n)
+    w = 1 << 20
+    for first in (0, (n // 2) + 12345, n - w):
+        got = dev.download(dy + 4 * first, w, np.float32)
+        x = sm.fill_host(w, 0xB0070001, 0, 0, first=first)
+        y = sm.fill_host(w, 0xB0070001, 1, 0, first=first)
+        assert mismatches(got, oracle_lib.saxpy(y, x, 2.5)) == 0
+    dev.free(dx); dev.free(dy)
