@@ -1,0 +1,325 @@
+// gemm_tf32x3.cu -- fp32 GEMM C = A.B on the sm_100a tensor cores with 3xTF32.
+//
+// The contraction is the reference's matmul (tests/tri_matmul_k.py:8-23,
+// tests/canonical.cu:18-50): row-major fp32 A[M,K], B[K,N], C[M,N]. The tensor
+// cores multiply TF32 (10-bit mantissa) operands, so every fp32 operand is split
+// into hi = tf32(x) and lo = tf32(x - hi) and the product is rebuilt from three
+// MMAs accumulated in fp32 in tensor memory:
+//     a.b  ~=  a_lo.b_hi + a_hi.b_lo + a_hi.b_hi        (a_lo.b_lo ~ 2^-22 dropped)
+// which keeps the result within ~1e-6 of an fp32 GEMM.
+//
+// Three kernels:
+//   gemm_split_a    A[M,K]  -> A_hi, A_lo [M,K]            (elementwise, streaming)
+//   gemm_split_bt   B[K,N]  -> Bt_hi, Bt_lo [N,K]          (split + transpose through
+//                   shared memory, so both MMA operands are K-major)
+//   gemm_tf32x3     one 128 x BN tile of C per CTA:
+//       warp 0, one lane : TMA producer. cp.async.bulk.tensor (128-byte swizzle, no
+//                          multicast) brings the four operand tiles of a 32-wide
+//                          K block into a ring of shared-memory stages and signals
+//                          the stage's "full" mbarrier with the byte count.
+//       warp 1, one lane : MMA issuer. Per K block 4 x 3 tcgen05.mma.kind::tf32
+//                          (M=128, N=BN, K=8) into an fp32 accumulator of BN
+//                          columns in TMEM; tcgen05.commit releases the stage
+//                          ("empty" mbarrier) and, after each chunk of K, hands
+//                          the accumulator to the epilogue warps.
+//       warps 2-9        : running sum + epilogue. tcgen05.ld of each finished
+//                          chunk, fp32 round-to-nearest adds into registers, and
+//                          at the end 512-byte row segments stored to C.
+// Every mbarrier wait is bounded by a wall-clock limit (%globaltimer); on expiry
+// the kernel records a code in *status, lets copies in flight drain, frees its
+// TMEM and returns, so a logic error cannot hang the device.
+#include "common.cuh"
+#include <cuda.h>
+
+namespace gemm {
+
+constexpr int BM = 128;          // rows of C per CTA = TMEM lanes
+constexpr int BK = 32;           // fp32 per K block = one 128-byte swizzle row
+constexpr int UMMA_K = 8;        // K of one tcgen05.mma.kind::tf32
+constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ unsigned long long globaltimer()
+{
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count)
+{
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+// Bounded wait: false when the limit ran out (an error code has been recorded).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *status, int code)
+{
+    if (mbar_try_wait(bar, parity)) return true;
+    const unsigned long long t0 = globaltimer();
+    while (!mbar_try_wait(bar, parity)) {
+        if (globaltimer() - t0 > WAIT_LIMIT_NS) { atomicCAS(status, 0, code); return false; }
+    }
+    return true;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+
+// Shared-memory matrix descriptor for a K-major tile whose rows are 128 bytes,
+// 128-byte swizzle: 8-row groups are 1024 bytes apart (SBO), descriptor version 1.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr)
+{
+    return (uint64_t)((addr & 0x3FFFFu) >> 4) | ((uint64_t)(1024u >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: D = fp32, A = B = TF32, both K-major, M = 128, N = bn.
+__host__ __device__ constexpr uint32_t instr_desc(int bn)
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+}
+
+__device__ __forceinline__ void umma_tf32(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                 "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+
+__device__ __forceinline__ float to_tf32(float x)
+{
+    uint32_t r;
+    asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(x));
+    return __uint_as_float(r);
+}
+
+}  // namespace gemm
+
+// hi[i] = tf32(a[i]), lo[i] = tf32(a[i] - hi[i]); n is a multiple of 4.
+extern "C" __global__ void gemm_split_a(const float4 *__restrict__ a, float4 *__restrict__ hi,
+                                        float4 *__restrict__ lo, long long n4)
+{
+    const long long T = (long long)gridDim.x * blockDim.x;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += T) {
+        const float4 v = __ldcs(a + i);
+        float4 h, l;
+        h.x = gemm::to_tf32(v.x); l.x = gemm::to_tf32(v.x - h.x);
+        h.y = gemm::to_tf32(v.y); l.y = gemm::to_tf32(v.y - h.y);
+        h.z = gemm::to_tf32(v.z); l.z = gemm::to_tf32(v.z - h.z);
+        h.w = gemm::to_tf32(v.w); l.w = gemm::to_tf32(v.w - h.w);
+        hi[i] = h;
+        lo[i] = l;
+    }
+}
+
+// B[K,N] row-major -> hi/lo planes of B^T, [N,K] row-major. 32x32 tiles through
+// shared memory (padded against bank conflicts); block (32,8), grid (N/32, K/32).
+extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__restrict__ hi,
+                                         float *__restrict__ lo, int K, int N)
+{
+    __shared__ float tile[32][33];
+    const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
+    for (int r = threadIdx.y; r < 32; r += 8)
+        tile[r][threadIdx.x] = b[(long long)(k0 + r) * N + n0 + threadIdx.x];
+    __syncthreads();
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        const float v = tile[threadIdx.x][r];
+        const float h = gemm::to_tf32(v);
+        const long long o = (long long)(n0 + r) * K + k0 + threadIdx.x;
+        hi[o] = h;
+        lo[o] = gemm::to_tf32(v - h);
+    }
+}
+
+// One 128 x BN tile of C per CTA; grid (N/BN, M/128), 320 threads,
+// dynamic shared memory = STAGES * (2*128 + 2*BN) * 128 bytes + 1024 (alignment).
+//
+// Accumulation. The tensor core adds into its fp32 accumulator with truncation,
+// so one long accumulation over K drifts (measured: relative error ~7e-9 * K).
+// The K loop is therefore cut into chunks of CHUNK_KB K blocks (128 values of K):
+// each chunk is accumulated in TMEM starting from zero, then the eight epilogue
+// warps pull it into registers (tcgen05.ld) and add it to a running fp32 sum
+// with round-to-nearest adds on the CUDA cores. Two TMEM accumulators alternate,
+// so the MMA issuer starts the next chunk while the previous one is drained.
+template <int BN, int STAGES>
+__device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUtensorMap *map_a_lo,
+                                          const CUtensorMap *map_b_hi, const CUtensorMap *map_b_lo,
+                                          float *__restrict__ c, int N, int K, int *status)
+{
+    using namespace gemm;
+    constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
+    constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
+    constexpr int CHUNK_KB = 4;                 // K blocks per TMEM accumulation
+    constexpr int HALF = BN / 2;                // columns of C per epilogue warp
+    constexpr uint32_t TMEM_COLS = 2 * BN;      // two accumulators
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t s_tmem;
+
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;    // swizzle atoms are 1024-byte aligned
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+    const int nkb = K / BK;
+    const int nchunk = (nkb + CHUNK_KB - 1) / CHUNK_KB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 0) {        // one warp allocates the tensor memory columns
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        // ---- TMA producer (one lane) ----
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, status, 1)) break;
+                const uint32_t st = smem0 + (uint32_t)s * STAGE_BYTES, full = full0 + 8 * s;
+                mbar_expect_tx(full, STAGE_BYTES);
+                tma_load_2d(st, map_a_hi, full, kb * BK, m0);
+                tma_load_2d(st + A_BYTES, map_a_lo, full, kb * BK, m0);
+                tma_load_2d(st + 2 * A_BYTES, map_b_hi, full, kb * BK, n0);
+                tma_load_2d(st + 2 * A_BYTES + B_BYTES, map_b_lo, full, kb * BK, n0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer (one lane) ----
+        if (lane == 0) {
+            constexpr uint32_t idesc = instr_desc(BN);
+            bool ok = true;
+            int kb = 0;
+            for (int ch = 0; ch < nchunk && ok; ch++) {
+                const uint32_t buf = (uint32_t)ch & 1u;
+                ok = mbar_wait(acc_empty0 + 8 * buf, (((uint32_t)ch >> 1) & 1u) ^ 1u, status, 4);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tacc = tmem + buf * (uint32_t)BN;
+                const int kb_end = min(kb + CHUNK_KB, nkb);
+                for (bool first = true; kb < kb_end; kb++) {
+                    const int s = kb % STAGES;
+                    const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                    ok = mbar_wait(full0 + 8 * s, ph, status, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st = smem0 + (uint32_t)s * STAGE_BYTES;
+                    const uint64_t a_hi = smem_desc(st), a_lo = smem_desc(st + A_BYTES);
+                    const uint64_t b_hi = smem_desc(st + 2 * A_BYTES), b_lo = smem_desc(st + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);   // 32 bytes along K inside the swizzle row
+                        umma_tf32(tacc, a_lo + adv, b_hi + adv, idesc, first ? 0u : 1u);
+                        umma_tf32(tacc, a_hi + adv, b_lo + adv, idesc, 1u);
+                        umma_tf32(tacc, a_hi + adv, b_hi + adv, idesc, 1u);
+                        first = false;
+                    }
+                    umma_commit(empty0 + 8 * s);          // frees the stage once these MMAs have read it
+                }
+                umma_commit(acc_full0 + 8 * buf);         // arrives when the chunk's MMAs have finished
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- accumulate + epilogue: warps 2..9. Warp w may touch TMEM lanes
+        // 32*(w%4)..+31 (rows of the tile); warps 2-5 take the left half of the
+        // columns, warps 6-9 the right half. ----
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        float acc[HALF];
+#pragma unroll
+        for (int j = 0; j < HALF; j++) acc[j] = 0.0f;
+        bool ok = true;
+        for (int ch = 0; ch < nchunk; ch++) {
+            const uint32_t buf = (uint32_t)ch & 1u;
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full0 + 8 * buf, ((uint32_t)ch >> 1) & 1u, status, 3));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tsrc = tmem + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(h * HALF);
+#pragma unroll
+            for (int cc = 0; cc < HALF / 32; cc++) {
+                uint32_t r[32];
+                tmem_ld32(tsrc + (uint32_t)(cc * 32), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; j++) acc[cc * 32 + j] = __fadd_rn(acc[cc * 32 + j], __uint_as_float(r[j]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
+        }
+        if (__all_sync(0xffffffffu, ok && *(volatile int *)status == 0)) {
+            float4 *dst = reinterpret_cast<float4 *>(c + (long long)(m0 + q * 32 + lane) * N + n0 + h * HALF);
+#pragma unroll
+            for (int j = 0; j < HALF / 4; j++)
+                dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+        } else {
+            // A wait ran out: give copies that may still be in flight time to
+            // land before the shared memory is released.
+            for (int i = 0; i < 64; i++) __nanosleep(4000);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0)
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+extern "C" __global__ void __launch_bounds__(320, 1)
+gemm_tf32x3(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+            const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+            float *c, int N, int K, int *status)
+{
+    gemm_tile<256, 2>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status);
+}
+
+extern "C" __global__ void __launch_bounds__(320, 1)
+gemm_tf32x3_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                 float *c, int N, int K, int *status)
+{
+    gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status);
+}

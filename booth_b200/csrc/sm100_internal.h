@@ -53,6 +53,10 @@ typedef struct sm100_api {
 } sm100_api_t;
 
 #define SM100_TRAK_MAX 64
+/* Byte offsets inside the device scratch buffer. */
+#define SM100_SCRATCH_TICKET       0
+#define SM100_SCRATCH_GEMM_STATUS  128
+#define SM100_SCRATCH_PARTIALS     256
 
 /* Built-in kernels, resolved once per device from the embedded image. */
 enum {
@@ -60,7 +64,7 @@ enum {
     SM100_K_REDUCE_I32, SM100_K_REDUCE_F32,
     SM100_K_ASIAN_MC, SM100_K_ASIAN_MC_PRECISE,
     SM100_K_ASIAN_PATHS, SM100_K_ASIAN_PATHS_PRECISE,
-    SM100_K_GEMM_SPLIT_A, SM100_K_GEMM_SPLIT_BT, SM100_K_GEMM_TF32X3,
+    SM100_K_GEMM_SPLIT_A, SM100_K_GEMM_SPLIT_BT, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128,
     SM100_K_COUNT
 };
 
@@ -84,6 +88,8 @@ struct sm100_dev {
     /* GEMM workspace: the hi/lo planes of A and of B transposed. */
     CUdeviceptr gemm_ws;
     size_t      gemm_ws_bytes;
+    int         gemm_pending;          /* a GEMM was enqueued since the last status check */
+    int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
     /* bc_trak labels. */
     struct { unsigned long long ptr, size; char label[24]; int flags; } trak[SM100_TRAK_MAX];
     int         ntrak;
@@ -96,6 +102,8 @@ int  sm100_enter(sm100_dev_t *dev);
 /* Launch one of the built-in kernels on the device's stream. */
 int  sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
                     unsigned shmem, void **args);
+int  sm100_launch_k3(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsigned gz,
+                     unsigned bx, unsigned by, unsigned bz, unsigned shmem, void **args);
 /* Grows the device-owned scratch / GEMM workspace; returns 0 on failure. */
 CUdeviceptr sm100_scratch(sm100_dev_t *dev, size_t bytes);
 CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes);

@@ -35,9 +35,10 @@ static int bad_arg(sm100_dev_t *dev, const char *what)
     return SM100_ERR_ARG;
 }
 
-/* Scratch layout: the arrival counter in the first 256 bytes, partials after. */
-#define SCRATCH_TICKET   0
-#define SCRATCH_PARTIALS 256
+/* Scratch layout: the arrival counter and the GEMM status word in the first
+ * 256 bytes, partials after. */
+#define SCRATCH_TICKET   SM100_SCRATCH_TICKET
+#define SCRATCH_PARTIALS SM100_SCRATCH_PARTIALS
 
 /* Streaming kernels: 256-thread blocks, each block iteration covers
  * 256 threads x 4 x 16 bytes; the grid is a multiple of the SM count so every
@@ -318,11 +319,66 @@ void matmul_k(float *a, float *b, float *c, int K, int stride_am, int stride_ak,
                 stride_cm, stride_cn, 1, nthreads);
 }
 
+/* ---- fp32 GEMM, 3xTF32 on tcgen05 ---- */
+
+static int tmap_2d(sm100_dev_t *dev, CUtensorMap *map, CUdeviceptr base, int rows, int K, int box_rows)
+{
+    /* Row-major [rows][K] fp32; a box is 32 floats (one 128-byte swizzle row) wide. */
+    cuuint64_t dims[2] = { (cuuint64_t)K, (cuuint64_t)rows };
+    cuuint64_t strides[1] = { (cuuint64_t)K * 4 };
+    cuuint32_t box[2] = { 32, (cuuint32_t)box_rows };
+    cuuint32_t estr[2] = { 1, 1 };
+    CUresult cr = dev->api->TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void *)(uintptr_t)base,
+                                                 dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                                                 CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "cuTensorMapEncodeTiled", cr);
+}
+
 int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t b, int M, int N, int K)
 {
-    (void)c; (void)a; (void)b; (void)M; (void)N; (void)K;
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
-    fprintf(stderr, "sm100_rt: gemm_tf32x3 is not in this image\n");
-    return SM100_ERR_KERN;
+    if (!c || !a || !b || M <= 0 || N <= 0 || K <= 0 || (M % 128) || (N % 256) || (K % 32) || ((a | b | c) & 15))
+        return bad_arg(dev, "booth_sm100_gemm: need M % 128 == 0, N % 256 == 0, K % 32 == 0, 16-byte aligned pointers");
+    const int bn = env_int("BOOTH_SM100_GEMM_BN", 256, 128, 256) == 128 ? 128 : 256;
+    const size_t a_bytes = (size_t)M * K * 4, b_bytes = (size_t)N * K * 4;
+    CUdeviceptr ws = sm100_gemm_ws(dev, 2 * a_bytes + 2 * b_bytes);
+    if (!ws) return SM100_ERR_CUDA;
+    CUdeviceptr a_hi = ws, a_lo = ws + a_bytes, b_hi = ws + 2 * a_bytes, b_lo = b_hi + b_bytes;
+
+    /* 1. split A, split + transpose B */
+    long long n4 = (long long)M * K / 4;
+    void *sa[] = { &a, &a_hi, &a_lo, &n4 };
+    if ((rc = sm100_launch_k(dev, SM100_K_GEMM_SPLIT_A, (unsigned)dev->sm_count * 8, 256, 0, sa)) != SM100_OK) return rc;
+    void *sb[] = { &b, &b_hi, &b_lo, &K, &N };
+    if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(N / 32), (unsigned)(K / 32), 1, 32, 8, 1, 0, sb)) != SM100_OK)
+        return rc;
+
+    /* 2. the tiled contraction */
+    CUtensorMap maps[4];
+    if ((rc = tmap_2d(dev, &maps[0], a_hi, M, K, 128)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[1], a_lo, M, K, 128)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[2], b_hi, N, K, bn)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[3], b_lo, N, K, bn)) != SM100_OK) return rc;
+    const unsigned shmem = 197632;     /* stages * (2*128 + 2*bn) * 128 bytes + 1024: the same for both tile widths */
+    if (!dev->gemm_smem_set) {
+        CUresult cr = dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_TF32X3],
+                                                 CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
+        if (cr == CUDA_SUCCESS)
+            cr = dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_TF32X3_N128],
+                                            CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
+        if (cr != CUDA_SUCCESS) return sm100_fail(dev, "raising the GEMM kernel's shared memory limit", cr);
+        dev->gemm_smem_set = 1;
+    }
+    CUdeviceptr status = dev->scratch + SM100_SCRATCH_GEMM_STATUS;
+    if (!dev->gemm_pending) {
+        CUresult cr = dev->api->MemsetD8Async(status, 0, 4, dev->stream);
+        if (cr != CUDA_SUCCESS) return sm100_fail(dev, "clearing the GEMM status word", cr);
+    }
+    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &N, &K, &status };
+    rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3 : SM100_K_GEMM_TF32X3_N128,
+                         (unsigned)(N / bn), (unsigned)(M / 128), 1, 320, 1, 1, shmem, ga);
+    if (rc == SM100_OK) dev->gemm_pending = 1;
+    return rc;
 }

@@ -140,7 +140,7 @@ static const char *const k_names[SM100_K_COUNT] = {
     "reduce_sum_i32", "reduce_sum_f32",
     "asian_mc", "asian_mc_precise",
     "asian_paths", "asian_paths_precise",
-    "gemm_split_a", "gemm_split_bt", "gemm_tf32x3",
+    "gemm_split_a", "gemm_split_bt", "gemm_tf32x3", "gemm_tf32x3_n128",
 };
 
 int sm100_rt_device_count(void)
@@ -209,7 +209,6 @@ int sm100_rt_init(sm100_dev_t **out, int ordinal)
     }
     for (int i = 0; i < SM100_K_COUNT; i++) {
         cr = a->ModuleGetFunction(&d->k[i], d->image, k_names[i]);
-        if (cr != CUDA_SUCCESS && i >= SM100_K_GEMM_SPLIT_A) { d->k[i] = NULL; continue; }
         if (cr != CUDA_SUCCESS) {
             fprintf(stderr, "sm100_rt: built-in kernel '%s' missing from the image\n", k_names[i]);
             rc = SM100_ERR_KERN; goto drop_image;
@@ -519,19 +518,25 @@ int sm100_rt_launch_packed(sm100_dev_t *dev, const sm100_kern_t *kern,
     return SM100_OK;
 }
 
-int sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
-                   unsigned shmem, void **args)
+int sm100_launch_k3(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsigned gz,
+                    unsigned bx, unsigned by, unsigned bz, unsigned shmem, void **args)
 {
-    CUresult cr = dev->api->LaunchKernel(dev->k[which], grid, 1, 1, block, 1, 1,
+    CUresult cr = dev->api->LaunchKernel(dev->k[which], gx, gy, gz, bx, by, bz,
                                          shmem, dev->stream, args, NULL);
     if (cr != CUDA_SUCCESS) {
-        char what[128];
-        snprintf(what, sizeof what, "cuLaunchKernel '%s' grid %u block %u shmem %u",
-                 k_names[which], grid, block, shmem);
+        char what[160];
+        snprintf(what, sizeof what, "cuLaunchKernel '%s' grid %ux%ux%u block %ux%ux%u shmem %u",
+                 k_names[which], gx, gy, gz, bx, by, bz, shmem);
         return sm100_fail(dev, what, cr);
     }
     dev->launches++;
     return SM100_OK;
+}
+
+int sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
+                   unsigned shmem, void **args)
+{
+    return sm100_launch_k3(dev, which, grid, 1, 1, block, 1, 1, shmem, args);
 }
 
 int sm100_rt_sync(sm100_dev_t *dev)
@@ -540,6 +545,20 @@ int sm100_rt_sync(sm100_dev_t *dev)
     if (rc != SM100_OK) return rc;
     CUresult cr = dev->api->StreamSynchronize(dev->stream);
     if (cr != CUDA_SUCCESS) { rc = sm100_fail(dev, "sync", cr); dump_trak(dev); return rc; }
+    if (dev->gemm_pending) {
+        /* The GEMM kernel bounds its barrier waits and reports an expired one
+         * in a status word instead of hanging. */
+        int st = 0;
+        dev->gemm_pending = 0;
+        cr = dev->api->MemcpyDtoH(&st, dev->scratch + SM100_SCRATCH_GEMM_STATUS, sizeof st);
+        if (cr != CUDA_SUCCESS) return sm100_fail(dev, "reading GEMM status", cr);
+        if (st != 0) {
+            snprintf(dev->err, sizeof dev->err, "gemm_tf32x3 gave up waiting on a barrier (code %d: "
+                     "1 = producer, 2 = MMA issuer, 3 = epilogue)", st);
+            fprintf(stderr, "sm100_rt: %s\n", dev->err);
+            return SM100_ERR_CUDA;
+        }
+    }
     return SM100_OK;
 }
 

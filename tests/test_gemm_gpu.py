@@ -1,0 +1,92 @@
+"""GPU parity: fp32 GEMM (3xTF32 on tcgen05) against the CPU checker's tiled
+matmul (tests/tri_matmul_k.py called tile by tile). Relative Frobenius error
+<= 1e-5 over the compared rows."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5
+
+
+def rel_fro(got, want):
+    return float(np.linalg.norm(got.astype(np.float64) - want.astype(np.float64)) /
+                 np.linalg.norm(want.astype(np.float64)))
+
+
+def gpu_gemm(dev, a, b):
+    M, K = a.shape
+    _, N = b.shape
+    da, db, dc = dev.upload(a), dev.upload(b), dev.alloc(M * N * 4)
+    dev.gemm(dc, da, db, M, N, K)
+    dev.sync()
+    c = dev.download(dc, (M, N), np.float32)
+    for p in (da, db, dc):
+        dev.free(p)
+    return c
+
+
+def inputs(sm, M, N, K, seed=0xB0070003):
+    a = sm.fill_host(M * K, seed, 0, 0).reshape(M, K)
+    b = sm.fill_host(K * N, seed, 1, 0).reshape(K, N)
+    return a, b
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 256, 32), (128, 256, 64), (128, 256, 96), (256, 512, 256),
+                                   (384, 256, 1024), (512, 768, 512)])
+def test_gemm_matches_cpu_checker(sm, dev, oracle_lib, M, N, K):
+    a, b = inputs(sm, M, N, K)
+    got = gpu_gemm(dev, a, b)
+    want = oracle_lib.matmul(a, b)
+    assert rel_fro(got, want) <= TOL
+    # inject-must-fail: one wrong element in a 128x256 result is visible at this tolerance
+    bad = got.copy()
+    bad[M // 2, N // 3] += np.float32(1.0)
+    assert rel_fro(bad, want) > TOL
+
+
+def test_gemm_layout_identity_and_one_hot(sm, dev):
+    """Catches a swapped operand, a transposed tile or a swizzle mismatch exactly."""
+    M, N, K = 128, 256, 256
+    a = sm.fill_host(M * K, 17, 0, 0).reshape(M, K)
+    eye = np.eye(K, N, dtype=np.float32)
+    got = gpu_gemm(dev, a, eye)
+    assert np.allclose(got, a, rtol=0, atol=2e-7)
+    # B = shifted permutation with distinct weights
+    perm = np.zeros((K, N), np.float32)
+    cols = (np.arange(K) * 7 + 3) % N
+    perm[np.arange(K), cols] = np.arange(1, K + 1, dtype=np.float32)
+    got = gpu_gemm(dev, a, perm)
+    want = (a.astype(np.float64) @ perm.astype(np.float64))
+    assert np.allclose(got, want, rtol=1e-6, atol=1e-6)
+
+
+def test_gemm_argument_errors(sm, dev):
+    p = dev.alloc(1 << 20)
+    for M, N, K in ((100, 256, 32), (128, 200, 32), (128, 256, 30), (0, 256, 32)):
+        with pytest.raises(sm.Sm100Error) as e:
+            dev.gemm(p, p, p, M, N, K)
+        assert e.value.code == sm.ERR_ARG
+    dev.free(p)
+
+
+@pytest.mark.parametrize("size", [4096, 8192])
+def test_gemm_full_size_sampled_rows(sm, dev, oracle_lib, size):
+    """M = N = K in {4096, 8192}: inputs generated on the device from the seeded
+    stream, the CPU checker computes a seeded sample of 4-row blocks of C from
+    the same stream generated on the host (rows of C are independent given B)."""
+    M = N = K = size
+    da, db, dc = dev.alloc(M * K * 4), dev.alloc(K * N * 4), dev.alloc(M * N * 4)
+    dev.fill(da, 0, M * K, 0xB0070003, 0, 0)
+    dev.fill(db, 0, K * N, 0xB0070003, 1, 0)
+    dev.gemm(dc, da, db, M, N, K)
+    dev.sync()
+    rng = np.random.default_rng(size)
+    rows4 = np.sort(rng.choice(M // 4, size=32 if size == 8192 else 64, replace=False)).astype(np.int32)
+    a, b = inputs(sm, M, N, K)
+    want = oracle_lib.matmul(a, b, rows4=rows4)
+    rows = (rows4[:, None] * 4 + np.arange(4)[None, :]).ravel()
+    got = np.stack([dev.download(dc + int(r) * N * 4, N, np.float32) for r in rows])
+    assert rel_fro(got, want[rows]) <= TOL
+    for p in (da, db, dc):
+        dev.free(p)
