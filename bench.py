@@ -55,58 +55,71 @@ def measured_peaks():
 
 
 class ClockSampler:
-    """Samples nvidia-smi clocks and throttle reasons while a timed region runs."""
-    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock, power and throttle reasons through NVML (read-only) every
+    few milliseconds while a timed region runs; nvidia-smi is the fallback."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
 
-    def __init__(self, index):
-        self.index = index
-        self.rows = []
-        self.proc = None
-        self.thread = None
+    def __init__(self, index, period_s=0.004):
+        self.index, self.period = index, period_s
+        self.rows, self.stop_flag, self.thread, self.nvml = [], threading.Event(), None, None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nvml = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.sm_max = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nvml = None
 
     def start(self):
-        try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.FIELDS,
-                 "--format=csv,noheader,nounits", "-lms", "200"],
-                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            self.proc = None
+        self.rows, self.stop_flag = [], threading.Event()
+        if self.nvml is None:
             return
         self.thread = threading.Thread(target=self._pump, daemon=True)
         self.thread.start()
 
     def _pump(self):
-        for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+        n = self.nvml
+        while not self.stop_flag.is_set():
+            try:
+                sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+                pw = n.nvmlDeviceGetPowerUsage(self.handle) / 1000.0
+                try:
+                    rs = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                except Exception:
+                    rs = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+                self.rows.append((sm, pw, rs))
+            except Exception:
+                pass
+            time.sleep(self.period)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            self.proc.wait(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
+        if self.nvml is None:
+            return self._smi_once()
+        self.stop_flag.set()
         self.thread.join(timeout=5)
-        sm, smax, power, reasons = [], [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for r in self.rows:
-            if len(r) < 9:
-                continue
-            try:
-                sm.append(float(r[1])); smax.append(float(r[2])); power.append(float(r[3]))
-            except ValueError:
-                continue
-            for name, val in zip(names, r[5:9]):
-                if val.lower().startswith("active"):
-                    reasons.add(name)
-        if not sm:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["no samples"]}
-        return {"sm_mhz": float(np.median(sm)), "sm_max_mhz": max(smax), "power_w_max": max(power),
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if not self.rows:
+            return {"sm_mhz": None, "sm_max_mhz": float(self.sm_max), "reasons": ["no samples"]}
+        reasons = sorted(name for name, bit in self.REASONS if any(r[2] & bit for r in self.rows))
+        return {"sm_mhz": float(np.median([r[0] for r in self.rows])), "sm_max_mhz": float(self.sm_max),
+                "sm_min_mhz": float(min(r[0] for r in self.rows)), "power_w_max": max(r[1] for r in self.rows),
+                "samples": len(self.rows), "reasons": reasons, "source": "nvml"}
+
+    def _smi_once(self):
+        fields = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+                  "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+                  "clocks_event_reasons.sw_power_cap")
+        try:
+            out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + fields,
+                                  "--format=csv,noheader,nounits"], stdout=subprocess.PIPE, text=True, timeout=20).stdout
+            r = [c.strip() for c in out.strip().split(",")]
+            names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+            return {"sm_mhz": float(r[0]), "sm_max_mhz": float(r[1]), "power_w_max": float(r[2]), "samples": 1,
+                    "reasons": [n for n, v in zip(names, r[3:7]) if v.lower().startswith("active")],
+                    "source": "nvidia-smi after the timed region"}
+        except Exception as e:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable: %s" % e]}
 
 
 class Ranks:
@@ -210,10 +223,13 @@ def run_ours(args):
     head_roof["frac_of_nominal_8TBs"] = per_gpu / 8000.0
 
     # ---- e2e: the launcher API with host buffers (the examples/launch_saxpy.c flow) ----
-    e2e = run_e2e_saxpy(sm, dev, ranks, n, max(1, min(K, args.e2e_steps)))
+    e2e = None if args.no_e2e else run_e2e_saxpy(sm, dev, ranks, n, max(1, min(K, args.e2e_steps)))
+    want = set(args.workloads.split(",")) if args.workloads != "all" else {"sweep", "vadd", "reduce", "asian", "gemm"}
+    if args.headline_only:
+        want = set()
 
     # ---- size sweep (config 1) and vector add (config 0) ----
-    if not args.headline_only:
+    if "sweep" in want:
         sweep = []
         for lg in range(20, args.log2n + 1, 2):
             m = 1 << lg
@@ -221,7 +237,8 @@ def run_ours(args):
             sweep.append({"log2n": lg, "ms": t, "gbs_per_gpu": 12.0 * m / (t * 1e-3) / 1e9})
         workloads.append({"name": "saxpy_sweep", "unit": "GB/s per GPU", "note": "sizes below ~2^25 fit the 126 MB L2",
                           "points": sweep})
-        for lg in (LOG2_VADD, 28):
+    if "vadd" in want:
+        for lg in (LOG2_VADD, min(28, args.log2n)):
             m = 1 << lg
             dz = dev.alloc(m * 4)
             t = timed(dev, ranks, W, K, lambda: dev.vadd(dx, dy, dz, m)) / K
@@ -232,8 +249,9 @@ def run_ours(args):
                               "note": "201 MB working set, partly L2-resident" if lg == LOG2_VADD else "3 GiB working set"})
             dev.free(dz)
 
+    out = dev.alloc(64)
+    if "reduce" in want:
         # ---- reduction (config 2): per-GPU sum then one NCCL all-reduce ----
-        out = dev.alloc(64)
         for name, kind, fn, dt in (("reduce_i32", sm.FILL_I32_1000, dev.reduce_i32, sm.I32),
                                    ("reduce_f32", sm.FILL_F32_01, dev.reduce_f32, sm.F64)):
             dev.fill(dx, first, n, SEED + 2, 0 if dt == sm.I32 else 1, kind)
@@ -249,6 +267,7 @@ def run_ours(args):
                               "ms_per_step": t, "result": float(res), "allreduce": bool(comm),
                               "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s", None, peaks)})
 
+    if "asian" in want:
         # ---- Asian-option Monte Carlo (config 4): disjoint Philox subsequences per GPU ----
         npaths = 1 << args.log2paths
         for precise in (0, 1):
@@ -270,8 +289,10 @@ def run_ours(args):
                               "stderr_geom": disc * math.sqrt(max(s[3] / tot - (s[1] / tot) ** 2, 0.0) / tot),
                               "allreduce": bool(comm)})
 
+    if "gemm" in want:
         # ---- fp32 GEMM (config 3): row blocks of A per GPU, B replicated ----
-        workloads.extend(run_gemm(sm, dev, ranks, peaks, W, K))
+        sizes = [int(v) for v in args.gemm_sizes.split(",")]
+        workloads.extend(run_gemm(sm, dev, ranks, peaks, W, K, sizes))
 
     line = {
         "metric": "saxpy_hbm_gbs", "value": saxpy_gbs, "unit": "GB/s", "n_gpus": G, "steps": K, "warmup": W,
@@ -343,12 +364,12 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps):
             "api": "bc_copy_h2d x2 + bc_dispatch(saxpy) + bc_copy_d2h, pinned host buffers, synchronous"}
 
 
-def run_gemm(sm, dev, ranks, peaks, W, K):
+def run_gemm(sm, dev, ranks, peaks, W, K, sizes):
     out = []
     G = ranks.world
     # 3xTF32: three TF32 MMAs per fp32 product; TF32 dense rate is half the bf16 rate.
     peak = peaks["bf16_tflops"] / 2.0 / 3.0
-    for size in GEMM_SIZES:
+    for size in sizes:
         M = size // G
         if M % 128:
             continue
@@ -437,6 +458,10 @@ def main():
     ap.add_argument("--e2e-steps", type=int, default=5)
     ap.add_argument("--cpu-seconds", type=float, default=12.0)
     ap.add_argument("--headline-only", action="store_true", help="skip the other workloads")
+    ap.add_argument("--workloads", default="all",
+                    help="comma list of the extra workloads to run: sweep,vadd,reduce,asian,gemm (default all)")
+    ap.add_argument("--gemm-sizes", default=",".join(str(v) for v in GEMM_SIZES))
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     if args.impl == "reference":
