@@ -314,7 +314,7 @@ def run_ours(args):
         comm.close()
     dev.close()
     if ranks.rank == 0:
-        print(json.dumps(line), flush=True)
+        emit(line)
     ranks.close()
 
 
@@ -444,7 +444,20 @@ def run_reference(args):
             "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": orc.cores, "kind": orc.kind,
                              "sample": "2^28 elements per step, %d threads over disjoint ranges" % orc.cores},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
-    print(json.dumps(line), flush=True)
+    emit(line)
+
+
+def emit(line):
+    """The one JSON line, on the process's real stdout."""
+    os.write(_REAL_STDOUT, (json.dumps(line) + "\n").encode())
+
+
+# Libraries (NCCL prints its version) may write to stdout; the contract is ONE JSON
+# line there. File descriptor 1 is pointed at stderr for the whole run and the
+# line goes to a saved copy of the original stdout.
+sys.stdout.flush()
+_REAL_STDOUT = os.dup(1)
+os.dup2(2, 1)
 
 
 def main():
