@@ -40,13 +40,16 @@ static int bad_arg(sm100_dev_t *dev, const char *what)
 #define SCRATCH_TICKET   SM100_SCRATCH_TICKET
 #define SCRATCH_PARTIALS SM100_SCRATCH_PARTIALS
 
-/* Streaming kernels: 256-thread blocks, each block iteration covers
- * 256 threads x 4 x 16 bytes; the grid is a multiple of the SM count so every
- * SM carries the same number of resident blocks, capped by the work there is. */
-static unsigned stream_grid(sm100_dev_t *dev, long long n, unsigned block, unsigned unroll)
+/* Streaming kernels: 128-thread blocks, `dflt` of them per SM; one block
+ * iteration covers 128 threads x 2 x 32 bytes per input. HBM throughput on a
+ * B200 peaks sharply at about 80 KB of loads in flight per SM (measured for
+ * saxpy at 2^30 elements: 5.8 TB/s at 3 blocks per SM, 6.5 at 4, 6.9 at 5, 6.7 at
+ * 6, 6.5 at 8 and above), so the grid is that small multiple of the SM count,
+ * capped by the work there is. BOOTH_SM100_STREAM_BPSM / _BLOCK override it. */
+static unsigned stream_grid(sm100_dev_t *dev, long long n, unsigned block, unsigned unroll, int dflt)
 {
-    const int bpsm = env_int("BOOTH_SM100_STREAM_BPSM", 8, 1, 64);
-    long long tiles = ((n >> 2) + (long long)block * unroll - 1) / ((long long)block * unroll);
+    const int bpsm = env_int("BOOTH_SM100_STREAM_BPSM", dflt, 1, 64);
+    long long tiles = ((n >> 3) + (long long)block * unroll - 1) / ((long long)block * unroll);
     long long g = (long long)dev->sm_count * bpsm;
     if (tiles < g) g = tiles;
     if (g < 1) g = 1;
@@ -74,9 +77,9 @@ int booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y, sm100_ptr_t
     if (n < 0 || n > INT_MAX) return bad_arg(dev, "booth_sm100_vadd: n must be in [0, 2^31)");
     if (n == 0) return SM100_OK;
     int ni = (int)n, bs = 256;
-    const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 256, 32, 1024);
+    const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &x, &y, &out, &ni, &bs };
-    return sm100_launch_k(dev, SM100_K_VADD, stream_grid(dev, n, block, 4), block, 0, args);
+    return sm100_launch_k(dev, SM100_K_VADD, stream_grid(dev, n, block, 2, 5), block, 0, args);
 }
 
 int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, long long n)
@@ -86,18 +89,22 @@ int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, l
     if (n < 0 || n > INT_MAX) return bad_arg(dev, "booth_sm100_saxpy: n must be in [0, 2^31)");
     if (n == 0) return SM100_OK;
     int ni = (int)n;
-    const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 256, 32, 1024);
+    const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &y, &x, &a, &ni };
-    return sm100_launch_k(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 4), block, 0, args);
+    return sm100_launch_k(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 2, 5), block, 0, args);
 }
 
-static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long n, sm100_ptr_t out)
+/* Reductions: 256-thread blocks, eight 16-byte loads per thread in flight. The
+ * int32 kernel (32 registers) runs best at 6 blocks per SM (7.1 TB/s at 2^30
+ * elements against 6.6 at 4); the fp32 kernel (54 registers, at most 4 blocks
+ * fit an SM) at 4 (7.0 TB/s). BOOTH_SM100_REDUCE_BPSM / _BLOCK override. */
+static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long n, sm100_ptr_t out, int dflt_bpsm)
 {
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
     if (n < 0 || !out || (in & 3)) return bad_arg(dev, "booth_sm100_reduce: bad argument");
     const unsigned block = (unsigned)env_int("BOOTH_SM100_REDUCE_BLOCK", 256, 32, 1024) & ~31u;
-    const int bpsm = env_int("BOOTH_SM100_REDUCE_BPSM", 4, 1, 32);
+    const int bpsm = env_int("BOOTH_SM100_REDUCE_BPSM", dflt_bpsm, 1, 32);
     long long tiles = ((n >> 2) + (long long)block * 8 - 1) / ((long long)block * 8);
     long long g = (long long)dev->sm_count * bpsm;
     if (tiles < g) g = tiles;
@@ -111,12 +118,12 @@ static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long 
 
 int booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
 {
-    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out);
+    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out, 6);
 }
 
 int booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
 {
-    return reduce_common(dev, SM100_K_REDUCE_F32, in, n, out);
+    return reduce_common(dev, SM100_K_REDUCE_F32, in, n, out, 4);
 }
 
 int booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
