@@ -93,6 +93,7 @@ _SIGNATURES = {
     "booth_sm100_saxpy": (C.c_int, [_dev, _ptr, _ptr, C.c_float, C.c_longlong]),
     "booth_sm100_reduce_i32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
     "booth_sm100_reduce_f32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
+    "booth_sm100_reduce_f32_noalloc": (C.c_int, [_ptr, C.c_longlong, _ptr, C.c_void_p]),
     "booth_sm100_gemm": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_int, C.c_int, C.c_int]),
     "booth_sm100_asian": (C.c_int, [_dev, C.POINTER(AsianParams), C.c_longlong, C.c_longlong, _ptr]),
     "booth_sm100_asian_paths": (C.c_int, [_dev, C.POINTER(AsianParams), C.c_longlong, C.c_longlong, _ptr, _ptr]),

@@ -5,8 +5,10 @@
 Steps:
   1. nvcc -gencode arch=compute_100a,code=sm_100a -cubin  csrc/kernels/image.cu
         -> lib/booth_sm100.cubin   (also the file bc_load_kernel is pointed at)
-  2. gcc -std=c99 -shared  csrc/*.c csrc/image.S (embeds the cubin)
-        -> lib/libbooth_sm100.so   (links libdl/libpthread only; libcuda and
+  2. nvcc -c  csrc/reduce_noalloc.cu  (the one runtime-API translation unit:
+        its scratch is a __device__ array, so it carries its own device code)
+  3. gcc -std=c99 -shared  csrc/*.c csrc/image.S (embeds the cubin) + that object
+        -> lib/libbooth_sm100.so   (static cudart, libdl, libpthread; libcuda and
                                     libnccl are opened at run time)
 nvcc cross-compiles without a GPU. Outputs are git-ignored build products.
 """
@@ -66,15 +68,21 @@ def build(force=False, verbose=False):
         with open(os.path.join(LIB, "ptxas.log"), "w") as f:
             f.write(log[-1])
     csrc = [os.path.join(CSRC, f) for f in C_SOURCES]
-    deps = csrc + [CUBIN, os.path.join(CSRC, "image.S"), os.path.join(CSRC, "sm100_internal.h"),
+    noalloc_cu = os.path.join(CSRC, "reduce_noalloc.cu")
+    noalloc_o = os.path.join(LIB, "reduce_noalloc.o")
+    if force or not _newer(noalloc_o, [noalloc_cu, os.path.join(INCLUDE, "booth_sm100.h")]):
+        _run([os.path.join(cuda, "bin", "nvcc"), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
+              "-std=c++17", "-Xcompiler", "-fPIC", "-I", INCLUDE, "-c", noalloc_cu, "-o", noalloc_o], log)
+    deps = csrc + [noalloc_o, CUBIN, os.path.join(CSRC, "image.S"), os.path.join(CSRC, "sm100_internal.h"),
                    os.path.join(INCLUDE, "booth_sm100.h"), os.path.join(INCLUDE, "bc_runtime.h")]
     if force or not _newer(SO, deps):
         _run(["gcc", "-std=c99", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra",
               "-Wno-unused-parameter", "-fvisibility=default",
               "-I", INCLUDE, "-I", CSRC, "-I", os.path.join(cuda, "include"),
               '-DBOOTH_SM100_IMAGE="%s"' % CUBIN,
-              "-o", SO] + csrc + [os.path.join(CSRC, "image.S")] +
-             ["-Wl,-Bsymbolic", "-Wl,-z,noexecstack", "-ldl", "-lpthread"], log)
+              "-o", SO] + csrc + [os.path.join(CSRC, "image.S"), noalloc_o] +
+             ["-Wl,-Bsymbolic", "-Wl,-z,noexecstack", "-Wl,--exclude-libs,ALL", "-L", os.path.join(cuda, "lib64"), "-lcudart_static",
+              "-lstdc++", "-lrt", "-ldl", "-lpthread"], log)
     if verbose:
         sys.stdout.write("\n".join(log))
     return SO

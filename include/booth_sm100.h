@@ -161,6 +161,17 @@ int  booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
  * sums, combined in double. The workload's fp32 answer is (float)out[0]. */
 int  booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
                             sm100_ptr_t out);
+/* The fp32 sum again, for callers that may not allocate device memory (no
+ * cudaMalloc inside a frozen memory pool, in a real-time loop, or in a plug-in whose
+ * host owns the GPU's memory). It takes no device handle: it runs on the CUDA
+ * runtime's current device and on `stream` (a cudaStream_t, NULL for the default
+ * stream) and keeps its segment sums in a 33,024-byte array built into the
+ * library, so n is limited to 2^30 elements; larger n returns SM100_ERR_ARG.
+ * out[0] (double, device memory) receives the sum. The first call on a device
+ * resolves the array's address and loads the library's device code there: make
+ * it before any stream capture. Calls share the array: do not let two of them
+ * overlap on the GPU. This entry point has no counterpart in the reference. */
+int  booth_sm100_reduce_f32_noalloc(sm100_ptr_t in, long long n, sm100_ptr_t out, void *stream);
 /* C[M,N] = A[M,K] * B[K,N], row-major fp32, 3xTF32 on the tensor cores:
  * the tests/tri_matmul_k.py:8-23 / tests/canonical.cu:18-50 contraction.
  * M % 128 == 0, N % 256 == 0, K % 32 == 0. */
