@@ -134,7 +134,7 @@ int booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
     if (!p || !out || npaths < 0 || path0 < 0 || p->nstep <= 0 || (p->nstep & 3))
         return bad_arg(dev, "booth_sm100_asian: bad argument (nstep must be a positive multiple of 4)");
     const unsigned block = 256;
-    const int bpsm = env_int("BOOTH_SM100_ASIAN_BPSM", 4, 1, 8);
+    const int bpsm = env_int("BOOTH_SM100_ASIAN_BPSM", 8, 1, 16);
     long long g = (npaths + block - 1) / block;
     if (g > (long long)dev->sm_count * bpsm) g = (long long)dev->sm_count * bpsm;
     if (g < 1) g = 1;
