@@ -119,3 +119,44 @@ def test_shard_range_covers_and_aligns(sm):
             assert spans[0][0] == 0 and spans[-1][1] == n
             for (lo, hi), (lo2, _) in zip(spans, spans[1:]):
                 assert hi == lo2 and lo <= hi and lo % 4 == 0 and hi % 4 == 0
+
+
+def test_run_side_descriptor_mirrors_the_reference_contract(sm, tmp_path):
+    """include/rt_sm100.h declares rt_desc_t on its own; its layout and status
+    codes must be those of the reference's src/exec/exec.h (checked by compiling a
+    probe against each header when the reference tree is present), and the
+    library must export a descriptor with every required operation filled in."""
+    handle = C.CDLL(sm.LIB_PATH)
+    desc = C.c_void_p.in_dll(handle, "rt_sm100")          # the exported object exists
+    words = (C.c_uint64 * 18).from_address(C.addressof(desc))
+    assert C.string_at(words[0]) == b"sm100" and C.string_at(words[1]) == b"cubin"
+    dev_size, kern_size = words[2] & 0xFFFFFFFF, words[2] >> 32
+    assert 0 < dev_size <= 1024 and 0 < kern_size <= 192   # RT_DEV_MAX / RT_KERN_MAX (src/exec/exec.h:43-44)
+    assert all(words[i] != 0 for i in range(3, 17))        # 10 required + 4 optional operations
+    ref_hdr = "/root/reference/src/exec/exec.h"
+    if not os.path.exists(ref_hdr):
+        return
+    probe = r"""
+#include <stdio.h>
+#include <stddef.h>
+#ifdef REF
+#include "exec.h"
+#else
+#include "rt_sm100.h"
+#endif
+int main(void){
+  printf("%zu %zu %zu %zu ", sizeof(rt_desc_t), sizeof(rt_arg_t), sizeof(rt_dim_t), sizeof(rt_ptr));
+  printf("%zu %zu %zu %zu %zu %zu ", offsetof(rt_desc_t,dev_size), offsetof(rt_desc_t,open), offsetof(rt_desc_t,run),
+         offsetof(rt_desc_t,sync), offsetof(rt_desc_t,hmap), offsetof(rt_desc_t,errs));
+  printf("%d %d %d %d %d %d %d %d %d %d %d\n", RT_OK, RT_ENODRV, RT_ESYM, RT_EDRV, RT_ENODEV, RT_EIO, RT_EKERN,
+         RT_EUNSUP, RT_EINPUT, RT_DEV_MAX, RT_KERN_MAX);
+  return 0; }
+"""
+    src = tmp_path / "probe.c"
+    src.write_text(probe)
+    outs = []
+    for flags in (["-DREF", "-I", os.path.dirname(ref_hdr)], ["-I", os.path.join(ROOT, "include")]):
+        exe = tmp_path / ("probe_" + str(len(outs)))
+        subprocess.run(["gcc", "-std=c99"] + flags + [str(src), "-o", str(exe)], check=True)
+        outs.append(subprocess.run([str(exe)], stdout=subprocess.PIPE, text=True, check=True).stdout)
+    assert outs[0] == outs[1], outs

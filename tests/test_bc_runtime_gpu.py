@@ -114,10 +114,15 @@ EXAMPLES = os.path.join(ROOT, "build", "examples")
     ("launch_saxpy", True, "PASS: all 1024 elements correct"),
     ("cpu_launch_vadd", False, "OK: Triton vector_add ran"),
     ("cpu_launch_matmul", False, "OK: Triton matmul ran"),
+    ("rt_sm100_run", True, "PASS: descriptor 'sm100' (cubin) ran saxpy"),
+    ("rt_sm100_run_refhdr", True, "PASS: descriptor 'sm100' (cubin) ran saxpy"),
 ])
 def test_reference_example_programs_relinked(sm, prog, needs_cubin, expect):
     """The reference's own example sources, compiled unchanged where they lie in
-    the reference tree and linked against libbooth_sm100 by the build step."""
+    the reference tree and linked against libbooth_sm100 by the build step; and
+    this repository's rt_sm100_run, which drives the GPU through the run-side
+    descriptor contract (src/exec/exec.h:69-93), built once on the mirror header
+    and once on the reference's own exec.h."""
     exe = os.path.join(EXAMPLES, prog)
     if not os.path.exists(exe):
         pytest.skip("build/examples/%s was not built (the reference tree was absent at build time)" % prog)
