@@ -116,6 +116,7 @@ EXAMPLES = os.path.join(ROOT, "build", "examples")
     ("cpu_launch_matmul", False, "OK: Triton matmul ran"),
     ("rt_sm100_run", True, "PASS: descriptor 'sm100' (cubin) ran saxpy"),
     ("rt_sm100_run_refhdr", True, "PASS: descriptor 'sm100' (cubin) ran saxpy"),
+    ("launch_workloads", False, "PASS: "),
 ])
 def test_reference_example_programs_relinked(sm, prog, needs_cubin, expect):
     """The reference's own example sources, compiled unchanged where they lie in
