@@ -323,3 +323,215 @@ gemm_tf32x3_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
 {
     gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status);
 }
+
+
+// ---------------------------------------------------------------------------
+// Two-CTA form: a cluster of two CTAs on neighbouring SMs computes one 256 x 256
+// tile of C with tcgen05.mma.cta_group::2 (M = 256, N = 256, K = 8).
+//
+//   CTA r of the pair loads the 128 rows r*128.. of the A tile and the 128 rows
+//   (values of n) r*128.. of the B^T tile, hi and lo planes: 64 KB per 32-wide K
+//   block, so three stages fit where the one-CTA form has two, and every operand
+//   byte that crosses L2 -> SM feeds 256 x 256 instead of 128 x 256 products.
+//   Both producers signal the LEADER's "full" barrier (cp.async.bulk.tensor with
+//   .cta_group::2 lets the completion land on the peer's mbarrier; no multicast).
+//   The leader's single MMA thread issues for the pair; tcgen05.commit with
+//   .multicast::cluster releases the stage in both CTAs and hands each CTA its
+//   half of the accumulator (rows r*128.. live in CTA r's tensor memory).
+//   Each CTA's warps 2-9 drain their own TMEM into register sums exactly as in
+//   the one-CTA form; the peer's warps arrive on the leader's "accumulator empty"
+//   barrier through its shared::cluster address.
+// All waits stay bounded; both CTAs meet at a cluster barrier before any of them
+// frees tensor memory or exits, so neither touches the other's shared memory
+// after it is gone.
+namespace gemm {
+
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t local_addr, uint32_t rank)
+{
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_addr), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The destination is this CTA's shared memory; the completion is counted on
+// `bar`, a shared::cluster address that may belong to the peer CTA.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, uint32_t bar, int x, int y)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void umma_tf32_pair(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the barrier at this shared-memory offset in both CTAs of the pair.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(bar), "h"((uint16_t)3) : "memory");
+}
+__host__ __device__ constexpr uint32_t instr_desc_pair(int bn)     // M = 256 across the pair
+{
+    return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+}  // namespace gemm
+
+// grid.x = 2 * (M/256) * (N/256), clusters of 2 along x, 320 threads,
+// dynamic shared memory = 3 * 64 KB + 1024.
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                 float *__restrict__ c, int N, int K, int *status)
+{
+    using namespace gemm;
+    constexpr int BN = 256, HALF_N = 128, STAGES = 3;
+    constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = HALF_N * BK * 4;
+    constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;          // per CTA
+    constexpr int CHUNK_KB = 4;
+    constexpr int HALF = BN / 2;                                         // columns per epilogue warp
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t s_tmem;
+
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const uint32_t smem0 = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_n = N / BN;
+    const int tile = blockIdx.x >> 1;
+    const int m0 = (tile / tiles_n) * 256 + (int)rank * BM;             // this CTA's rows of A and C
+    const int n0 = (tile % tiles_n) * BN;
+    const int nb0 = n0 + (int)rank * HALF_N;                            // this CTA's rows of B^T
+    const int nkb = K / BK;
+    const int nchunk = (nkb + CHUNK_KB - 1) / CHUNK_KB;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 16); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 1) {        // the same warp in both CTAs allocates for the pair
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();     // both CTAs' barriers are initialised before anyone signals them
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+
+    if (warp == 0) {
+        // ---- TMA producer, one lane in each CTA; completions count on the leader's barrier ----
+        if (lane == 0) {
+            for (int kb = 0; kb < nkb; kb++) {
+                const int s = kb % STAGES;
+                const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, status, 1)) break;
+                const uint32_t st = smem0 + (uint32_t)s * STAGE_BYTES;
+                const uint32_t full_leader = map_to_cta(full0 + 8 * s, 0);
+                if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                tma_load_2d_pair(st, &map_a_hi, full_leader, kb * BK, m0);
+                tma_load_2d_pair(st + A_BYTES, &map_a_lo, full_leader, kb * BK, m0);
+                tma_load_2d_pair(st + 2 * A_BYTES, &map_b_hi, full_leader, kb * BK, nb0);
+                tma_load_2d_pair(st + 2 * A_BYTES + B_BYTES, &map_b_lo, full_leader, kb * BK, nb0);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer: one lane of the leader CTA issues for the pair ----
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = instr_desc_pair(BN);
+            bool ok = true;
+            int kb = 0;
+            for (int ch = 0; ch < nchunk && ok; ch++) {
+                const uint32_t buf = (uint32_t)ch & 1u;
+                ok = mbar_wait(acc_empty0 + 8 * buf, (((uint32_t)ch >> 1) & 1u) ^ 1u, status, 4);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tacc = tmem + buf * (uint32_t)BN;
+                const int kb_end = min(kb + CHUNK_KB, nkb);
+                for (bool first = true; kb < kb_end; kb++) {
+                    const int s = kb % STAGES;
+                    const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
+                    ok = mbar_wait(full0 + 8 * s, ph, status, 2);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t st = smem0 + (uint32_t)s * STAGE_BYTES;
+                    const uint64_t a_hi = smem_desc(st), a_lo = smem_desc(st + A_BYTES);
+                    const uint64_t b_hi = smem_desc(st + 2 * A_BYTES), b_lo = smem_desc(st + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; k++) {
+                        const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+                        umma_tf32_pair(tacc, a_lo + adv, b_hi + adv, idesc, first ? 0u : 1u);
+                        umma_tf32_pair(tacc, a_hi + adv, b_lo + adv, idesc, 1u);
+                        umma_tf32_pair(tacc, a_hi + adv, b_hi + adv, idesc, 1u);
+                        first = false;
+                    }
+                    umma_commit_pair(empty0 + 8 * s);          // frees the stage in both CTAs
+                }
+                umma_commit_pair(acc_full0 + 8 * buf);         // each CTA's half of the chunk is complete
+            }
+        }
+        __syncwarp();
+    } else {
+        // ---- running sum + epilogue, as in the one-CTA form, on this CTA's 128 rows ----
+        const int q = warp & 3, h = (warp - 2) >> 2;
+        float acc[HALF];
+#pragma unroll
+        for (int j = 0; j < HALF; j++) acc[j] = 0.0f;
+        bool ok = true;
+        for (int ch = 0; ch < nchunk; ch++) {
+            const uint32_t buf = (uint32_t)ch & 1u;
+            ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full0 + 8 * buf, ((uint32_t)ch >> 1) & 1u, status, 3));
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t tsrc = tmem + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(h * HALF);
+#pragma unroll
+            for (int cc = 0; cc < HALF / 32; cc++) {
+                uint32_t r[32];
+                tmem_ld32(tsrc + (uint32_t)(cc * 32), r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 32; j++) acc[cc * 32 + j] = __fadd_rn(acc[cc * 32 + j], __uint_as_float(r[j]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty0 + 8 * buf, 0));   // the leader counts both CTAs
+        }
+        if (__all_sync(0xffffffffu, ok && *(volatile int *)status == 0)) {
+            float4 *dst = reinterpret_cast<float4 *>(c + (long long)(m0 + q * 32 + lane) * N + n0 + h * HALF);
+#pragma unroll
+            for (int j = 0; j < HALF / 4; j++)
+                dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+        } else {
+            for (int i = 0; i < 64; i++) __nanosleep(4000);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();     // nobody frees or exits while the peer may still signal or read
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}

@@ -140,7 +140,7 @@ static const char *const k_names[SM100_K_COUNT] = {
     "reduce_sum_i32", "reduce_sum_f32",
     "asian_mc", "asian_mc_precise",
     "asian_paths", "asian_paths_precise",
-    "gemm_split_a", "gemm_split_bt", "gemm_tf32x3", "gemm_tf32x3_n128",
+    "gemm_split_a", "gemm_split_bt", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta",
 };
 
 int sm100_rt_device_count(void)
@@ -554,7 +554,7 @@ int sm100_rt_sync(sm100_dev_t *dev)
         if (cr != CUDA_SUCCESS) return sm100_fail(dev, "reading GEMM status", cr);
         if (st != 0) {
             snprintf(dev->err, sizeof dev->err, "gemm_tf32x3 gave up waiting on a barrier (code %d: "
-                     "1 = producer, 2 = MMA issuer, 3 = epilogue)", st);
+                     "1 = producer, 2 = MMA issuer on operands, 3 = epilogue, 4 = MMA issuer on a free accumulator)", st);
             fprintf(stderr, "sm100_rt: %s\n", dev->err);
             return SM100_ERR_CUDA;
         }
