@@ -24,6 +24,9 @@ typedef struct sm100_api {
     CUresult (*FuncGetAttribute)(int *, CUfunction_attribute, CUfunction);
     CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int);
     CUresult (*FuncGetParamInfo)(CUfunction, size_t, size_t *, size_t *);   /* optional */
+    CUresult (*ModuleGetFunctionCount)(unsigned int *, CUmodule);           /* optional */
+    CUresult (*ModuleEnumerateFunctions)(CUfunction *, unsigned int, CUmodule); /* optional */
+    CUresult (*FuncGetName)(const char **, CUfunction);                     /* optional */
     CUresult (*MemAlloc)(CUdeviceptr *, size_t);
     CUresult (*MemFree)(CUdeviceptr);
     CUresult (*MemcpyHtoD)(CUdeviceptr, const void *, size_t);
@@ -90,6 +93,11 @@ struct sm100_dev {
     size_t      gemm_ws_bytes;
     int         gemm_pending;          /* a GEMM was enqueued since the last status check */
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
+    /* Snapshot of the most recent dispatch (kernel, geometry, first bytes of the
+     * parameter block), printed with the labelled buffers when a launch or the
+     * wait for it reports an error: the launcher's share of the reference's
+     * ABEND dump (src/runtime/bc_runtime.c:661-675, src/runtime/bc_abend.h:57-71). */
+    struct { char kernel[64]; unsigned grid[3], block[3], shmem, args_size, snap_size; unsigned char args[128]; int valid; } last;
     /* bc_trak labels. */
     struct { unsigned long long ptr, size; char label[24]; int flags; } trak[SM100_TRAK_MAX];
     int         ntrak;

@@ -63,6 +63,9 @@ static int api_load(void)
     SYM(FuncGetAttribute, "cuFuncGetAttribute");
     SYM(FuncSetAttribute, "cuFuncSetAttribute");
     OPT(FuncGetParamInfo, "cuFuncGetParamInfo");
+    OPT(ModuleGetFunctionCount, "cuModuleGetFunctionCount");
+    OPT(ModuleEnumerateFunctions, "cuModuleEnumerateFunctions");
+    OPT(FuncGetName, "cuFuncGetName");
     SYM(MemAlloc, "cuMemAlloc_v2");
     SYM(MemFree, "cuMemFree_v2");
     SYM(MemcpyHtoD, "cuMemcpyHtoD_v2");
@@ -285,11 +288,40 @@ static void kern_describe(sm100_dev_t *dev, sm100_kern_t *k)
     }
 }
 
+/* The launcher looks kernels up by their bare source name (src/runtime/bc_runtime.h:44-46).
+ * A cubin built by nvcc from a C++ source that does not say extern "C" carries
+ * the Itanium-mangled name instead (_Z<length><name><parameters>): when the bare
+ * name is absent, take the one kernel of the module whose mangled name starts
+ * with that prefix. */
+static int find_mangled(sm100_dev_t *dev, CUmodule mod, const char *name, CUfunction *out)
+{
+    const sm100_api_t *a = dev->api;
+    if (!a->ModuleGetFunctionCount || !a->ModuleEnumerateFunctions || !a->FuncGetName) return 0;
+    unsigned int count = 0;
+    if (a->ModuleGetFunctionCount(&count, mod) != CUDA_SUCCESS || count == 0 || count > 4096) return 0;
+    CUfunction *fs = (CUfunction *)malloc(count * sizeof *fs);
+    if (!fs) return 0;
+    char prefix[160];
+    int plen = snprintf(prefix, sizeof prefix, "_Z%zu%s", strlen(name), name);
+    int found = 0;
+    if (plen > 0 && plen < (int)sizeof prefix &&
+        a->ModuleEnumerateFunctions(fs, count, mod) == CUDA_SUCCESS) {
+        for (unsigned int i = 0; i < count; i++) {
+            const char *fn = NULL;
+            if (a->FuncGetName(&fn, fs[i]) != CUDA_SUCCESS || !fn) continue;
+            if (strncmp(fn, prefix, (size_t)plen) == 0) { *out = fs[i]; found++; }
+        }
+    }
+    free(fs);
+    return found == 1;
+}
+
 static int kern_from_module(sm100_dev_t *dev, CUmodule mod, int owns, const char *name,
                             sm100_kern_t *out)
 {
     CUfunction f;
     CUresult cr = dev->api->ModuleGetFunction(&f, mod, name);
+    if (cr != CUDA_SUCCESS && find_mangled(dev, mod, name, &f)) cr = CUDA_SUCCESS;
     if (cr != CUDA_SUCCESS) {
         snprintf(dev->err, sizeof dev->err, "kernel '%s' not found", name);
         fprintf(stderr, "sm100_rt: kernel '%s' not found in the image\n", name);
@@ -457,8 +489,30 @@ CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes)
 
 /* ---- launch ---- */
 
+static void snap_dispatch(sm100_dev_t *dev, const char *kernel, unsigned gx, unsigned gy, unsigned gz,
+                          unsigned bx, unsigned by, unsigned bz, unsigned shmem, const void *args, unsigned args_size)
+{
+    snprintf(dev->last.kernel, sizeof dev->last.kernel, "%s", kernel && *kernel ? kernel : "?");
+    dev->last.grid[0] = gx; dev->last.grid[1] = gy; dev->last.grid[2] = gz;
+    dev->last.block[0] = bx; dev->last.block[1] = by; dev->last.block[2] = bz;
+    dev->last.shmem = shmem;
+    dev->last.args_size = args_size;
+    dev->last.snap_size = args_size < sizeof dev->last.args ? args_size : (unsigned)sizeof dev->last.args;
+    if (args && dev->last.snap_size) memcpy(dev->last.args, args, dev->last.snap_size);
+    else dev->last.snap_size = 0;
+    dev->last.valid = 1;
+}
+
 static void dump_trak(sm100_dev_t *dev)
 {
+    if (dev->last.valid) {
+        fprintf(stderr, "sm100_rt:   last dispatch: kernel '%s' grid %ux%ux%u block %ux%ux%u shmem %u, %u parameter bytes:",
+                dev->last.kernel, dev->last.grid[0], dev->last.grid[1], dev->last.grid[2],
+                dev->last.block[0], dev->last.block[1], dev->last.block[2], dev->last.shmem, dev->last.args_size);
+        for (unsigned i = 0; i < dev->last.snap_size; i++)
+            fprintf(stderr, "%s%02x", (i % 8) ? "" : " ", dev->last.args[i]);
+        fprintf(stderr, "\n");
+    }
     for (int i = 0; i < dev->ntrak; i++)
         fprintf(stderr, "sm100_rt:   buffer '%s' at 0x%llx, %llu bytes\n",
                 dev->trak[i].label, dev->trak[i].ptr, dev->trak[i].size);
@@ -472,6 +526,7 @@ int sm100_rt_launch(sm100_dev_t *dev, const sm100_kern_t *kern,
     if (!kern || !kern->func) return fail_arg(dev, "sm100_rt_launch: no kernel");
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
+    snap_dispatch(dev, kern->name, gx, gy, gz, bx, by, bz, shmem, NULL, 0);
     CUresult cr = dev->api->LaunchKernel((CUfunction)kern->func, gx, gy, gz, bx, by, bz,
                                          shmem, dev->stream, args, NULL);
     if (cr != CUDA_SUCCESS) {
@@ -499,6 +554,7 @@ int sm100_rt_launch_packed(sm100_dev_t *dev, const sm100_kern_t *kern,
     if (want > sizeof block) return fail_arg(dev, "parameter block larger than 4096 bytes");
     memset(block, 0, want ? want : 1);
     if (args && args_size) memcpy(block, args, args_size < want ? args_size : want);
+    snap_dispatch(dev, kern->name, gx, gy, gz, bx, by, bz, shmem, block, (unsigned)want);
     void *extra[] = {
         CU_LAUNCH_PARAM_BUFFER_POINTER, block,
         CU_LAUNCH_PARAM_BUFFER_SIZE, &want,

@@ -132,3 +132,43 @@ def test_reference_example_programs_relinked(sm, prog, needs_cubin, expect):
                          env=dict(os.environ, LD_LIBRARY_PATH=os.path.dirname(sm.LIB_PATH)))
     assert res.returncode == 0, res.stdout + res.stderr
     assert expect in res.stdout
+
+
+def test_reference_sysprint_demo_relinked(sm):
+    """A second consumer of the bc_* API: the reference's SYSPRINT demo
+    (examples/launch_sysprint.c, runtime/sysprint.c) built unchanged against this
+    library; its kernel (examples/sysprint_kernel.cu) compiled by nvcc for sm_100a.
+    The kernel is a C++ symbol there, found by its bare name "sp_demo"."""
+    exe, cubin = os.path.join(EXAMPLES, "launch_sysprint"), os.path.join(EXAMPLES, "sp_demo.cubin")
+    if not (os.path.exists(exe) and os.path.exists(cubin)):
+        pytest.skip("build/examples/launch_sysprint was not built (the reference tree was absent at build time)")
+    res = subprocess.run([exe, cubin], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120,
+                         env=dict(os.environ, LD_LIBRARY_PATH=os.path.dirname(sm.LIB_PATH)))
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "DEMO.RESULT: sp_demo done" in res.stdout and "dropped: 0" in res.stdout
+
+
+def test_failed_launch_prints_dispatch_snapshot_and_labels(sm):
+    """The launcher's share of the reference's ABEND dump (src/runtime/bc_abend.h:57-71):
+    when the driver refuses a launch (a host-detected error: 2048 threads per block
+    exceed the limit, nothing reaches the GPU), stderr names the kernel, the
+    geometry, the parameter bytes and the buffers labelled with bc_trak."""
+    code = r"""
+import ctypes as C, booth_b200 as b
+L = b.lib(); d = b.BcDevice(); assert L.bc_device_init(C.byref(d)) == 0
+k = b.BcKernel(); assert L.bc_load_kernel(C.byref(d), b.CUBIN_PATH.encode(), b"saxpy", C.byref(k)) == 0
+p = L.bc_alloc(C.byref(d), 4096); L.bc_trak(C.byref(d), p, 4096, b"ybuf", 0)
+class A(C.Structure):
+    _fields_ = [("y", C.c_void_p), ("x", C.c_void_p), ("a", C.c_float), ("n", C.c_uint32)]
+a = A(p, p, 2.5, 16)
+rc = L.bc_dispatch(C.byref(d), C.byref(k), 1, 1, 1, 2048, 1, 1, C.byref(a), C.sizeof(a))
+print("rc", rc)
+a.n = 16
+print("rc_ok", L.bc_dispatch(C.byref(d), C.byref(k), 1, 1, 1, 256, 1, 1, C.byref(a), C.sizeof(a)))   # still usable
+L.bc_free(C.byref(d), p); L.bc_device_shutdown(C.byref(d))
+"""
+    res = subprocess.run([os.sys.executable, "-c", code], cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                         text=True, timeout=120)
+    assert "rc -3" in res.stdout and "rc_ok 0" in res.stdout, res.stdout + res.stderr
+    assert "last dispatch: kernel 'bc_dispatch' grid 1x1x1 block 2048x1x1" in res.stderr
+    assert "24 parameter bytes" in res.stderr and "buffer 'ybuf'" in res.stderr
