@@ -39,7 +39,7 @@ GEMM_SIZES = (4096, 8192)
 BYTES_PER_ELEM = {"saxpy": 12, "vadd": 12, "reduce": 4}
 # DRAM bytes per element per launch as counted by ncu (dram__bytes_read.sum +
 # dram__bytes_write.sum); see the summaries under profiles/. None = not captured.
-NCU_TRAFFIC_PER_ELEM = {"saxpy": None, "vadd": None, "reduce_i32": None, "reduce_f32": None}
+NCU_TRAFFIC_PER_ELEM = {"saxpy": 11.67, "vadd": 11.77, "reduce_i32": 4.03, "reduce_f32": 4.03}
 
 
 def measured_peaks():
@@ -182,6 +182,19 @@ def timed(dev, ranks, warmup, steps, body):
     return ranks.max(ms)
 
 
+def mufu_ceiling(path_steps_per_s, sm_count, clocks):
+    """The pricer is bound by the special-function unit, not by HBM or the tensor
+    pipe: 3 MUFU operations per path-step on 16 MUFU lanes per SM allow at most
+    16/3 path-steps per clock per SM. Reported per GPU at the SM clock sampled
+    during the timed region."""
+    mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz")
+    if not mhz:
+        return None
+    achieved = path_steps_per_s / (sm_count * mhz * 1e6)
+    return {"bound": "mufu issue", "achieved": achieved, "peak": 16.0 / 3.0, "unit": "path-steps/clk/SM",
+            "frac": achieved / (16.0 / 3.0), "sm_mhz": mhz}
+
+
 def roofline(bound, achieved, peak, unit, traffic, peaks):
     return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
             "frac": achieved / peak if peak else None, "traffic": traffic,
@@ -245,7 +258,8 @@ def run_ours(args):
             gbs = 12.0 * m / (t * 1e-3) / 1e9
             workloads.append({"name": "vadd_2^%d" % lg, "metric": "hbm_gbs", "value": gbs * G, "unit": "GB/s",
                               "ms_per_step": t,
-                              "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s", None, peaks),
+                              "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s",
+                                                   NCU_TRAFFIC_PER_ELEM["vadd"] * m if lg > 26 else None, peaks),
                               "note": "201 MB working set, partly L2-resident" if lg == LOG2_VADD else "3 GiB working set"})
             dev.free(dz)
 
@@ -265,7 +279,8 @@ def run_ours(args):
             gbs = 4.0 * n / (t * 1e-3) / 1e9
             workloads.append({"name": name + "_2^%d" % args.log2n, "metric": "hbm_gbs", "value": gbs * G, "unit": "GB/s",
                               "ms_per_step": t, "result": float(res), "allreduce": bool(comm),
-                              "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s", None, peaks)})
+                              "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s",
+                                                   NCU_TRAFFIC_PER_ELEM[name] * n, peaks)})
 
     if "asian" in want:
         # ---- Asian-option Monte Carlo (config 4): disjoint Philox subsequences per GPU ----
@@ -278,7 +293,10 @@ def run_ours(args):
                 dev.asian(prm, ranks.rank * npaths, npaths, out)
                 if comm:
                     comm.allreduce_sum(out, 4, sm.F64)
+            mc_sampler = ClockSampler(ranks.local)
+            mc_sampler.start()
             t = timed(dev, ranks, W if not precise else 1, ksteps, mc_step) / ksteps
+            mc_clocks = mc_sampler.stop()
             s = dev.download(out, 4, np.float64)
             tot = npaths * G
             disc = math.exp(-0.05)
@@ -287,7 +305,8 @@ def run_ours(args):
                               "path_steps_per_s": tot * NSTEP / (t * 1e-3), "ms_per_step": t,
                               "price_arith": disc * s[0] / tot, "price_geom": disc * s[1] / tot,
                               "stderr_geom": disc * math.sqrt(max(s[3] / tot - (s[1] / tot) ** 2, 0.0) / tot),
-                              "allreduce": bool(comm)})
+                              "allreduce": bool(comm), "clocks": mc_clocks,
+                              "mufu_ceiling": mufu_ceiling(npaths * NSTEP / (t * 1e-3), dev.sm_count, mc_clocks)})
 
     if "gemm" in want:
         # ---- fp32 GEMM (config 3): row blocks of A per GPU, B replicated ----
