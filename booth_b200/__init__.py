@@ -91,6 +91,8 @@ _SIGNATURES = {
     "booth_sm100_fill_host": (None, [C.c_void_p, C.c_longlong, C.c_longlong, C.c_uint32, C.c_uint32, C.c_int, C.c_int]),
     "booth_sm100_vadd": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_longlong]),
     "booth_sm100_saxpy": (C.c_int, [_dev, _ptr, _ptr, C.c_float, C.c_longlong]),
+    "booth_sm100_vadd_host": (C.c_int, [_dev, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong]),
+    "booth_sm100_saxpy_host": (C.c_int, [_dev, C.c_void_p, C.c_void_p, C.c_float, C.c_longlong]),
     "booth_sm100_reduce_i32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
     "booth_sm100_reduce_f32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
     "booth_sm100_reduce_f32_noalloc": (C.c_int, [_ptr, C.c_longlong, _ptr, C.c_void_p]),
@@ -254,6 +256,13 @@ class Device:
 
     def saxpy(self, y, x, a, n):
         self._ck("booth_sm100_saxpy", lib().booth_sm100_saxpy(self._h, y, x, a, n))
+
+    def saxpy_host(self, y_addr, x_addr, a, n):
+        """y = a*x + y on host vectors (addresses), pipelined over the link."""
+        self._ck("booth_sm100_saxpy_host", lib().booth_sm100_saxpy_host(self._h, y_addr, x_addr, a, n))
+
+    def vadd_host(self, x_addr, y_addr, out_addr, n):
+        self._ck("booth_sm100_vadd_host", lib().booth_sm100_vadd_host(self._h, x_addr, y_addr, out_addr, n))
 
     def reduce_i32(self, inp, n, out):
         self._ck("booth_sm100_reduce_i32", lib().booth_sm100_reduce_i32(self._h, inp, n, out))

@@ -39,6 +39,7 @@ typedef struct sm100_api {
     CUresult (*StreamCreate)(CUstream *, unsigned);
     CUresult (*StreamDestroy)(CUstream);
     CUresult (*StreamSynchronize)(CUstream);
+    CUresult (*StreamWaitEvent)(CUstream, CUevent, unsigned);
     CUresult (*EventCreate)(CUevent *, unsigned);
     CUresult (*EventDestroy)(CUevent);
     CUresult (*EventRecord)(CUevent, CUstream);
@@ -56,6 +57,8 @@ typedef struct sm100_api {
 } sm100_api_t;
 
 #define SM100_TRAK_MAX 64
+#define SM100_STAGE_SLOTS 3
+#define SM100_STAGE_BYTES (64u << 20)      /* one operand chunk: 16 Mi floats */
 /* Byte offsets inside the device scratch buffer. */
 #define SM100_SCRATCH_TICKET       0
 #define SM100_SCRATCH_GEMM_STATUS  128
@@ -91,6 +94,12 @@ struct sm100_dev {
     /* GEMM workspace: the hi/lo planes of A and of B transposed. */
     CUdeviceptr gemm_ws;
     size_t      gemm_ws_bytes;
+    /* Host-pointer streaming (booth_sm100_*_host): a ring of device staging slots, a
+     * second stream for the copies back, and one event pair per slot. */
+    CUstream    stream_out;
+    CUdeviceptr stage;                 /* SM100_STAGE_SLOTS x 2 x SM100_STAGE_BYTES */
+    CUevent     ev_computed[SM100_STAGE_SLOTS], ev_drained[SM100_STAGE_SLOTS];
+    int         stage_ready;
     int         gemm_pending;          /* a GEMM was enqueued since the last status check */
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
     /* Snapshot of the most recent dispatch (kernel, geometry, first bytes of the

@@ -225,6 +225,71 @@ void booth_sm100_fill_host(void *dst, long long first, long long n, uint32_t see
     for (int t = 1; t < threads; t++) pthread_join(tid[t], NULL);
 }
 
+/* ---- host-pointer streaming: H2D, kernel and D2H pipelined over chunks ---- */
+
+static int stage_setup(sm100_dev_t *dev)
+{
+    if (dev->stage_ready) return SM100_OK;
+    const sm100_api_t *a = dev->api;
+    CUresult cr = a->StreamCreate(&dev->stream_out, CU_STREAM_NON_BLOCKING);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "cuStreamCreate(copy-back stream)", cr);
+    for (int i = 0; i < SM100_STAGE_SLOTS && cr == CUDA_SUCCESS; i++) {
+        cr = a->EventCreate(&dev->ev_computed[i], CU_EVENT_DISABLE_TIMING);
+        if (cr == CUDA_SUCCESS) cr = a->EventCreate(&dev->ev_drained[i], CU_EVENT_DISABLE_TIMING);
+    }
+    if (cr == CUDA_SUCCESS) cr = a->MemAlloc(&dev->stage, (size_t)SM100_STAGE_SLOTS * 2 * SM100_STAGE_BYTES);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "setting up the staging ring", cr);
+    dev->stage_ready = 1;
+    return SM100_OK;
+}
+
+/* out[i] = op(x[i], y[i]) for host vectors. The vectors are cut into chunks of
+ * 16 Mi elements; chunk i+1 is on its way to the device (H2D on the compute
+ * stream) while chunk i is computed and chunk i-1 travels back (D2H on a second
+ * stream), so both directions of the link are busy. Three staging slots of
+ * 2 x 64 MiB on the device; a slot is reused once its copy back has finished. */
+static int stream_host(sm100_dev_t *dev, int saxpy, const float *x, const float *y, float *out, float a, long long n)
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (n < 0 || (n > 0 && (!x || !y || !out))) return bad_arg(dev, "booth_sm100_*_host: bad argument");
+    if (n == 0) return SM100_OK;
+    if ((rc = stage_setup(dev)) != SM100_OK) return rc;
+    const sm100_api_t *api = dev->api;
+    const long long chunk = SM100_STAGE_BYTES / 4;
+    CUresult cr = CUDA_SUCCESS;
+    long long done = 0;
+    for (long long i = 0; done < n && cr == CUDA_SUCCESS; i++, done += chunk) {
+        const int slot = (int)(i % SM100_STAGE_SLOTS);
+        const long long m = n - done < chunk ? n - done : chunk;
+        const CUdeviceptr dx = dev->stage + (size_t)slot * 2 * SM100_STAGE_BYTES, dy = dx + SM100_STAGE_BYTES;
+        if (i >= SM100_STAGE_SLOTS) cr = api->StreamWaitEvent(dev->stream, dev->ev_drained[slot], 0);
+        if (cr == CUDA_SUCCESS) cr = api->MemcpyHtoDAsync(dx, x + done, (size_t)m * 4, dev->stream);
+        if (cr == CUDA_SUCCESS) cr = api->MemcpyHtoDAsync(dy, y + done, (size_t)m * 4, dev->stream);
+        if (cr != CUDA_SUCCESS) break;
+        /* saxpy writes y in place; vector add writes its sum over the staged y */
+        rc = saxpy ? booth_sm100_saxpy(dev, dy, dx, a, m) : booth_sm100_vadd(dev, dx, dy, dy, m);
+        if (rc != SM100_OK) return rc;
+        cr = api->EventRecord(dev->ev_computed[slot], dev->stream);
+        if (cr == CUDA_SUCCESS) cr = api->StreamWaitEvent(dev->stream_out, dev->ev_computed[slot], 0);
+        if (cr == CUDA_SUCCESS) cr = api->MemcpyDtoHAsync(out + done, dy, (size_t)m * 4, dev->stream_out);
+        if (cr == CUDA_SUCCESS) cr = api->EventRecord(dev->ev_drained[slot], dev->stream_out);
+    }
+    if (cr == CUDA_SUCCESS) cr = api->StreamSynchronize(dev->stream_out);
+    if (cr == CUDA_SUCCESS) cr = api->StreamSynchronize(dev->stream);
+    return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "host-pointer streaming", cr);
+}
+
+int booth_sm100_saxpy_host(sm100_dev_t *dev, float *y, const float *x, float a, long long n)
+{
+    return stream_host(dev, 1, x, y, y, a, n);
+}
+
+int booth_sm100_vadd_host(sm100_dev_t *dev, const float *x, const float *y, float *out, long long n)
+{
+    return stream_host(dev, 0, x, y, out, 0.0f, n);
+}
+
 /* ---- CPU-launcher symbols ---- */
 
 static sm100_dev_t *g_host_dev;
@@ -255,13 +320,7 @@ void vector_add(float *x, float *y, float *out, int n_elements, int block_size, 
     (void)n_elements; (void)block_size;
     if (nthreads <= 0) return;
     sm100_dev_t *d = host_dev("vector_add");
-    size_t bytes = (size_t)nthreads * sizeof(float);
-    sm100_ptr_t dx = sm100_rt_alloc(d, bytes), dy = sm100_rt_alloc(d, bytes), dz = sm100_rt_alloc(d, bytes);
-    if (!dx || !dy || !dz) host_die("vector_add (alloc)");
-    if (sm100_rt_h2d(d, dx, x, bytes) || sm100_rt_h2d(d, dy, y, bytes) ||
-        booth_sm100_vadd(d, dx, dy, dz, nthreads) || sm100_rt_d2h(d, out, dz, bytes))
-        host_die("vector_add");
-    sm100_rt_free(d, dx); sm100_rt_free(d, dy); sm100_rt_free(d, dz);
+    if (booth_sm100_vadd_host(d, x, y, out, nthreads) != SM100_OK) host_die("vector_add");
 }
 
 void saxpy(float *y, float *x, float a, int n, int nthreads)
@@ -270,13 +329,7 @@ void saxpy(float *y, float *x, float a, int n, int nthreads)
     long long m = nthreads < n ? nthreads : n;
     if (m <= 0) return;
     sm100_dev_t *d = host_dev("saxpy");
-    size_t bytes = (size_t)m * sizeof(float);
-    sm100_ptr_t dx = sm100_rt_alloc(d, bytes), dy = sm100_rt_alloc(d, bytes);
-    if (!dx || !dy) host_die("saxpy (alloc)");
-    if (sm100_rt_h2d(d, dx, x, bytes) || sm100_rt_h2d(d, dy, y, bytes) ||
-        booth_sm100_saxpy(d, dy, dx, a, m) || sm100_rt_d2h(d, y, dy, bytes))
-        host_die("saxpy");
-    sm100_rt_free(d, dx); sm100_rt_free(d, dy);
+    if (booth_sm100_saxpy_host(d, y, x, a, m) != SM100_OK) host_die("saxpy");
 }
 
 /* Extent, in floats, of a strided 4 x K (or K x 4) operand starting at its base. */

@@ -78,6 +78,7 @@ static int api_load(void)
     SYM(StreamCreate, "cuStreamCreate");
     SYM(StreamDestroy, "cuStreamDestroy_v2");
     SYM(StreamSynchronize, "cuStreamSynchronize");
+    SYM(StreamWaitEvent, "cuStreamWaitEvent");
     SYM(EventCreate, "cuEventCreate");
     SYM(EventDestroy, "cuEventDestroy_v2");
     SYM(EventRecord, "cuEventRecord");
@@ -250,6 +251,12 @@ void sm100_rt_shut(sm100_dev_t *dev)
     const sm100_api_t *a = dev->api;
     if (a->CtxSetCurrent(dev->ctx) == CUDA_SUCCESS) {
         a->StreamSynchronize(dev->stream);
+        if (dev->stage_ready) {
+            a->StreamSynchronize(dev->stream_out);
+            for (int i = 0; i < SM100_STAGE_SLOTS; i++) { a->EventDestroy(dev->ev_computed[i]); a->EventDestroy(dev->ev_drained[i]); }
+            a->StreamDestroy(dev->stream_out);
+            a->MemFree(dev->stage);
+        }
         if (dev->gemm_ws) a->MemFree(dev->gemm_ws);
         if (dev->scratch) a->MemFree(dev->scratch);
         a->ModuleUnload(dev->image);

@@ -152,6 +152,15 @@ int  booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y,
  * tests/canonical.cu:168-173 as compiled by src/cpu/cpu_emit.c:538-542. */
 int  booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x,
                        float a, long long n);
+/* The same two operations on HOST vectors: chunks of 16 Mi elements are copied
+ * in, computed and copied back in a three-slot pipeline on two streams, so the
+ * host-to-device and device-to-host directions of the link overlap. These calls
+ * return when the result is in host memory. Page-locked host memory
+ * (sm100_rt_hostalloc) runs at link speed; pageable memory works, staged by the
+ * driver. They are what the CPU-launcher symbols vector_add and saxpy call
+ * (examples/cpu_launch_vadd.c:35 hands host arrays to the kernel). */
+int  booth_sm100_vadd_host(sm100_dev_t *dev, const float *x, const float *y, float *out, long long n);
+int  booth_sm100_saxpy_host(sm100_dev_t *dev, float *y, const float *x, float a, long long n);
 /* Sum of n int32 with wrapping arithmetic into *out (one int32 on the device):
  * the tg_reduce / reduce_sum shape, tests/tg_reduce.cu:4-26,
  * tests/canonical.cu:59-108. */

@@ -125,3 +125,28 @@ def test_full_size_saxpy_windows(sm, dev, oracle_lib):
         y = sm.fill_host(w, 0xB0070001, 1, 0, first=first)
         assert mismatches(got, oracle_lib.saxpy(y, x, 2.5)) == 0
     dev.free(dx); dev.free(dy)
+
+
+def test_host_vector_calls_pipeline_over_chunks(sm, dev, oracle_lib):
+    """booth_sm100_saxpy_host / _vadd_host: host vectors longer than two staging
+    chunks (16 Mi elements each), pageable and page-locked, bit-exact."""
+    n = (1 << 25) + (1 << 22) + 3                     # 2 full chunks + a ragged third
+    x = sm.fill_host(n, 31, 0, 0); y = sm.fill_host(n, 31, 1, 0)
+    want_s = oracle_lib.saxpy(y, x, 2.5); want_v = oracle_lib.vadd(x, y)
+    out = np.empty_like(x)
+    dev.vadd_host(x.ctypes.data, y.ctypes.data, out.ctypes.data, n)
+    assert mismatches(out, want_v) == 0
+    yy = y.copy()
+    dev.saxpy_host(yy.ctypes.data, x.ctypes.data, 2.5, n)
+    assert mismatches(yy, want_s) == 0
+    # page-locked buffers, reused slots on a second call
+    hx, hy = dev.hostalloc(n * 4), dev.hostalloc(n * 4)
+    import ctypes as C
+    C.memmove(hx, x.ctypes.data, n * 4)
+    for _ in range(2):
+        C.memmove(hy, y.ctypes.data, n * 4)
+        dev.saxpy_host(hy, hx, 2.5, n)
+        got = np.frombuffer((C.c_float * n).from_address(hy), dtype=np.float32)
+        assert mismatches(got.copy(), want_s) == 0
+    dev.hostfree(hx); dev.hostfree(hy)
+    dev.vadd_host(x.ctypes.data, y.ctypes.data, out.ctypes.data, 0)        # empty input is a no-op
