@@ -86,6 +86,7 @@ _SIGNATURES = {
     "sm100_rt_tic": (C.c_int, [_dev]),
     "sm100_rt_toc": (C.c_int, [_dev, C.POINTER(C.c_float)]),
     "sm100_rt_launches": (C.c_ulonglong, [_dev]),
+    "sm100_rt_stream": (C.c_void_p, [_dev]),
     # layer 2
     "booth_sm100_fill": (C.c_int, [_dev, _ptr, C.c_longlong, C.c_longlong, C.c_uint32, C.c_uint32, C.c_int]),
     "booth_sm100_fill_host": (None, [C.c_void_p, C.c_longlong, C.c_longlong, C.c_uint32, C.c_uint32, C.c_int, C.c_int]),
@@ -179,6 +180,11 @@ class Device:
     @property
     def sm_count(self):
         return lib().sm100_rt_sm_count(self._h)
+
+    @property
+    def stream(self):
+        """The CUstream this device's work runs on, as an integer handle."""
+        return lib().sm100_rt_stream(self._h)
 
     @property
     def launches(self):

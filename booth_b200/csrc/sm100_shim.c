@@ -273,6 +273,7 @@ int sm100_rt_sm_count(const sm100_dev_t *dev) { return dev ? dev->sm_count : 0; 
 int sm100_rt_ordinal(const sm100_dev_t *dev) { return dev ? dev->ordinal : -1; }
 const char *sm100_rt_errs(const sm100_dev_t *dev) { return dev ? dev->err : ""; }
 unsigned long long sm100_rt_launches(const sm100_dev_t *dev) { return dev ? dev->launches : 0; }
+void *sm100_rt_stream(const sm100_dev_t *dev) { return dev ? (void *)dev->stream : NULL; }
 
 /* ---- kernels ---- */
 
@@ -416,8 +417,12 @@ int sm100_rt_h2d(sm100_dev_t *dev, sm100_ptr_t dst, const void *src, size_t size
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
     if (size == 0) return SM100_OK;
-    CUresult cr = dev->api->StreamSynchronize(dev->stream);
-    if (cr == CUDA_SUCCESS) cr = dev->api->MemcpyHtoD((CUdeviceptr)dst, src, size);
+    /* Ordered on the device's own stream and complete on return. A plain
+     * cuMemcpyHtoD from pageable memory may return while the DMA is still in
+     * flight on the NULL stream, which this non-blocking stream does not wait
+     * for: a kernel launched right after could read stale data. */
+    CUresult cr = dev->api->MemcpyHtoDAsync((CUdeviceptr)dst, src, size, dev->stream);
+    if (cr == CUDA_SUCCESS) cr = dev->api->StreamSynchronize(dev->stream);
     return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "h2d copy", cr);
 }
 
@@ -426,8 +431,8 @@ int sm100_rt_d2h(sm100_dev_t *dev, void *dst, sm100_ptr_t src, size_t size)
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
     if (size == 0) return SM100_OK;
-    CUresult cr = dev->api->StreamSynchronize(dev->stream);
-    if (cr == CUDA_SUCCESS) cr = dev->api->MemcpyDtoH(dst, (CUdeviceptr)src, size);
+    CUresult cr = dev->api->MemcpyDtoHAsync(dst, (CUdeviceptr)src, size, dev->stream);
+    if (cr == CUDA_SUCCESS) cr = dev->api->StreamSynchronize(dev->stream);
     return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "d2h copy", cr);
 }
 

@@ -122,6 +122,9 @@ void sm100_rt_hostfree(sm100_dev_t *dev, void *hp);
  * a second one, waits for it and returns the milliseconds between the two. */
 int  sm100_rt_tic(sm100_dev_t *dev);
 int  sm100_rt_toc(sm100_dev_t *dev, float *ms);
+/* The stream all of this device's work is enqueued on (a CUstream / cudaStream_t),
+ * for callers that want to order their own work or copies with it. */
+void *sm100_rt_stream(const sm100_dev_t *dev);
 /* Number of kernel launches this device has enqueued since sm100_rt_init. */
 unsigned long long sm100_rt_launches(const sm100_dev_t *dev);
 

@@ -150,3 +150,27 @@ def test_host_vector_calls_pipeline_over_chunks(sm, dev, oracle_lib):
         assert mismatches(got.copy(), want_s) == 0
     dev.hostfree(hx); dev.hostfree(hy)
     dev.vadd_host(x.ctypes.data, y.ctypes.data, out.ctypes.data, 0)        # empty input is a no-op
+
+
+def test_empty_and_maximum_sizes(sm, dev, oracle_lib):
+    """n = 0 is a no-op; n = 2^31 - 1 (the largest the kernels' int parameter holds,
+    8 GiB per vector) is checked on windows at both ends; n = 2^31 is refused."""
+    p = dev.alloc(64)
+    dev.vadd(p, p, p, 0)
+    dev.saxpy(p, p, 2.5, 0)
+    with pytest.raises(sm.Sm100Error) as e:
+        dev.saxpy(p, p, 2.5, 1 << 31)
+    assert e.value.code == sm.ERR_ARG
+    with pytest.raises(sm.Sm100Error):
+        dev.vadd(p, p, p, -1)
+    dev.free(p)
+    n = (1 << 31) - 1
+    dx, dy = dev.alloc(n * 4), dev.alloc(n * 4)
+    dev.fill(dx, 0, n, 41, 0, 0); dev.fill(dy, 0, n, 41, 1, 0)
+    dev.saxpy(dy, dx, 2.5, n)
+    w = 1 << 18
+    for first in (0, n - w):
+        got = dev.download(dy + 4 * first, w, np.float32)
+        x = sm.fill_host(w, 41, 0, 0, first=first); y = sm.fill_host(w, 41, 1, 0, first=first)
+        assert mismatches(got, oracle_lib.saxpy(y, x, 2.5)) == 0
+    dev.free(dx); dev.free(dy)

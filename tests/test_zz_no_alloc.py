@@ -26,7 +26,9 @@ def regular(dev, p, n):
 
 
 def noalloc(sm, dev, p, n, out):
-    rc = sm.lib().booth_sm100_reduce_f32_noalloc(p, n, out, None)
+    # On the device's own stream, so the call is ordered after the upload of the
+    # input and before the copy that reads the result back.
+    rc = sm.lib().booth_sm100_reduce_f32_noalloc(p, n, out, dev.stream)
     assert rc == sm.OK
     return float(dev.download(out, 1, np.float64)[0])
 
