@@ -393,15 +393,18 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int bn)     // M = 256 ac
 
 }  // namespace gemm
 
-// grid.x = 2 * (M/256) * (N/256), clusters of 2 along x, 320 threads,
-// dynamic shared memory = 3 * 64 KB + 1024.
-extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
-gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *__restrict__ c, int N, int K, int *status)
+// grid.x = 2 * (M/256) * (N/BN), clusters of 2 along x, 320 threads, dynamic shared
+// memory = STAGES * (32 KB + BN * 128 B) + 1024. BN = 256 with 3 stages is the
+// form the host launches; BN = 128 with 4 stages is kept for experiments (it
+// fills the last wave of mid-sized problems but the narrower MMA measured 20 %
+// slower).
+template <int BN, int STAGES>
+__device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, const CUtensorMap &map_a_lo,
+                                               const CUtensorMap &map_b_hi, const CUtensorMap &map_b_lo,
+                                               float *__restrict__ c, int N, int K, int *status)
 {
     using namespace gemm;
-    constexpr int BN = 256, HALF_N = 128, STAGES = 3;
+    constexpr int HALF_N = BN / 2;
     constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = HALF_N * BK * 4;
     constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;          // per CTA
     constexpr int CHUNK_KB = 4;
@@ -534,4 +537,20 @@ gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_cons
     cluster_sync_all();     // nobody frees or exits while the peer may still signal or read
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                 const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                 float *__restrict__ c, int N, int K, int *status)
+{
+    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status);
+}
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
+gemm_tf32x3_2cta_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                      const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                      float *__restrict__ c, int N, int K, int *status)
+{
+    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status);
 }

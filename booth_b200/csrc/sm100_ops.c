@@ -401,9 +401,13 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     if (rc != SM100_OK) return rc;
     if (!c || !a || !b || M <= 0 || N <= 0 || K <= 0 || (M % 128) || (N % 256) || (K % 32) || ((a | b | c) & 15))
         return bad_arg(dev, "booth_sm100_gemm: need M % 128 == 0, N % 256 == 0, K % 32 == 0, 16-byte aligned pointers");
+    /* Two-CTA clusters whenever M allows; BOOTH_SM100_GEMM_2CTA=0 forces the one-CTA form. */
+    const int pair = (M % 256 == 0) && env_int("BOOTH_SM100_GEMM_2CTA", 1, 0, 1);
+    /* 256-wide tiles. The 128-wide forms (BOOTH_SM100_GEMM_BN=128) fill the last
+     * wave of mid-sized problems better but measured slower everywhere (4096^3:
+     * 184 against 226 TFLOP/s with CTA pairs): the narrower MMA re-reads A twice as
+     * often from shared memory. */
     const int bn = env_int("BOOTH_SM100_GEMM_BN", 256, 128, 256) == 128 ? 128 : 256;
-    /* Two-CTA clusters (256 x 256 tiles) whenever M allows; BOOTH_SM100_GEMM_2CTA=0 forces the one-CTA form. */
-    const int pair = (M % 256 == 0) && bn == 256 && env_int("BOOTH_SM100_GEMM_2CTA", 1, 0, 1);
     const size_t a_bytes = (size_t)M * K * 4, b_bytes = (size_t)N * K * 4;
     CUdeviceptr ws = sm100_gemm_ws(dev, 2 * a_bytes + 2 * b_bytes);
     if (!ws) return SM100_ERR_CUDA;
@@ -421,9 +425,9 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     CUtensorMap maps[4];
     if ((rc = tmap_2d(dev, &maps[0], a_hi, M, K, 128)) != SM100_OK) return rc;
     if ((rc = tmap_2d(dev, &maps[1], a_lo, M, K, 128)) != SM100_OK) return rc;
-    if ((rc = tmap_2d(dev, &maps[2], b_hi, N, K, pair ? 128 : bn)) != SM100_OK) return rc;
-    if ((rc = tmap_2d(dev, &maps[3], b_lo, N, K, pair ? 128 : bn)) != SM100_OK) return rc;
-    const unsigned shmem = 197632;     /* stages * (2*128 + 2*bn) * 128 bytes + 1024: the same for both tile widths */
+    if ((rc = tmap_2d(dev, &maps[2], b_hi, N, K, pair ? bn / 2 : bn)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[3], b_lo, N, K, pair ? bn / 2 : bn)) != SM100_OK) return rc;
+    const unsigned shmem = 197632;     /* stages * stage bytes + 1024: 2 x 96 KB, 3 x 64 KB or 4 x 48 KB, the same for every form */
     if (!dev->gemm_smem_set) {
         CUresult cr = dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_TF32X3],
                                                  CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
@@ -432,6 +436,9 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
                                             CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
         if (cr == CUDA_SUCCESS)
             cr = dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_TF32X3_2CTA],
+                                            CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
+        if (cr == CUDA_SUCCESS)
+            cr = dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_TF32X3_2CTA_N128],
                                             CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
         if (cr != CUDA_SUCCESS) return sm100_fail(dev, "raising the GEMM kernel's shared memory limit", cr);
         dev->gemm_smem_set = 1;
@@ -443,8 +450,8 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     }
     void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &N, &K, &status };
     if (pair)
-        rc = sm100_launch_k3(dev, SM100_K_GEMM_TF32X3_2CTA, 2u * (unsigned)(M / 256) * (unsigned)(N / 256), 1, 1,
-                             320, 1, 1, shmem, ga);
+        rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3_2CTA : SM100_K_GEMM_TF32X3_2CTA_N128,
+                             2u * (unsigned)(M / 256) * (unsigned)(N / bn), 1, 1, 320, 1, 1, shmem, ga);
     else
         rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3 : SM100_K_GEMM_TF32X3_N128,
                              (unsigned)(N / bn), (unsigned)(M / 128), 1, 320, 1, 1, shmem, ga);
