@@ -25,9 +25,12 @@
 //       warps 2-9        : running sum + epilogue. tcgen05.ld of each finished
 //                          chunk, fp32 round-to-nearest adds into registers, and
 //                          at the end 512-byte row segments stored to C.
-// Every mbarrier wait is bounded by a wall-clock limit (%globaltimer); on expiry
-// the kernel records a code in *status, lets copies in flight drain, frees its
-// TMEM and returns, so a logic error cannot hang the device.
+// Every mbarrier wait is bounded by a wall-clock limit (%globaltimer, wait_ns); on
+// expiry the kernel records a code in *status, lets copies in flight drain, frees
+// its TMEM and returns, so a logic error cannot hang the device. silent_producer
+// (host-side fault injection for the tests) keeps the TMA producer from issuing
+// anything, so the MMA issuer's and the epilogue's waits run out and exactly that
+// path is exercised.
 #include "common.cuh"
 #include <cuda.h>
 
@@ -36,7 +39,6 @@ namespace gemm {
 constexpr int BM = 128;          // rows of C per CTA = TMEM lanes
 constexpr int BK = 32;           // fp32 per K block = one 128-byte swizzle row
 constexpr int UMMA_K = 8;        // K of one tcgen05.mma.kind::tf32
-constexpr unsigned long long WAIT_LIMIT_NS = 4000000000ull;
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -64,13 +66,16 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
     return ok;
 }
+// Where a wait reports to and how long it may last.
+struct WaitCtl { int *status; unsigned long long limit_ns; };
+
 // Bounded wait: false when the limit ran out (an error code has been recorded).
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int *status, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtl &w, int code)
 {
     if (mbar_try_wait(bar, parity)) return true;
     const unsigned long long t0 = globaltimer();
     while (!mbar_try_wait(bar, parity)) {
-        if (globaltimer() - t0 > WAIT_LIMIT_NS) { atomicCAS(status, 0, code); return false; }
+        if (globaltimer() - t0 > w.limit_ns) { atomicCAS(w.status, 0, code); return false; }
     }
     return true;
 }
@@ -175,9 +180,11 @@ extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__r
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUtensorMap *map_a_lo,
                                           const CUtensorMap *map_b_hi, const CUtensorMap *map_b_lo,
-                                          float *__restrict__ c, int N, int K, int *status)
+                                          float *__restrict__ c, int N, int K, int *status_word,
+                                          unsigned long long wait_ns, int silent_producer)
 {
     using namespace gemm;
+    const WaitCtl status = { status_word, wait_ns };
     constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = BN * BK * 4;
     constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;
     constexpr int CHUNK_KB = 4;                 // K blocks per TMEM accumulation
@@ -213,7 +220,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
 
     if (warp == 0) {
         // ---- TMA producer (one lane) ----
-        if (lane == 0) {
+        if (lane == 0 && !silent_producer) {
             for (int kb = 0; kb < nkb; kb++) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
@@ -291,7 +298,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
             if (lane == 0)
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
         }
-        if (__all_sync(0xffffffffu, ok && *(volatile int *)status == 0)) {
+        if (__all_sync(0xffffffffu, ok && *(volatile int *)status_word == 0)) {
             float4 *dst = reinterpret_cast<float4 *>(c + (long long)(m0 + q * 32 + lane) * N + n0 + h * HALF);
 #pragma unroll
             for (int j = 0; j < HALF / 4; j++)
@@ -311,17 +318,17 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
 extern "C" __global__ void __launch_bounds__(320, 1)
 gemm_tf32x3(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
             const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-            float *c, int N, int K, int *status)
+            float *c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_tile<256, 2>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status);
+    gemm_tile<256, 2>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status, wait_ns, silent_producer);
 }
 
 extern "C" __global__ void __launch_bounds__(320, 1)
 gemm_tf32x3_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *c, int N, int K, int *status)
+                 float *c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status);
+    gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status, wait_ns, silent_producer);
 }
 
 
@@ -401,9 +408,11 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int bn)     // M = 256 ac
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, const CUtensorMap &map_a_lo,
                                                const CUtensorMap &map_b_hi, const CUtensorMap &map_b_lo,
-                                               float *__restrict__ c, int N, int K, int *status)
+                                               float *__restrict__ c, int N, int K, int *status_word,
+                                               unsigned long long wait_ns, int silent_producer)
 {
     using namespace gemm;
+    const WaitCtl status = { status_word, wait_ns };
     constexpr int HALF_N = BN / 2;
     constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = HALF_N * BK * 4;
     constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;          // per CTA
@@ -447,7 +456,7 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
 
     if (warp == 0) {
         // ---- TMA producer, one lane in each CTA; completions count on the leader's barrier ----
-        if (lane == 0) {
+        if (lane == 0 && !silent_producer) {
             for (int kb = 0; kb < nkb; kb++) {
                 const int s = kb % STAGES;
                 const uint32_t ph = (uint32_t)(kb / STAGES) & 1u;
@@ -523,7 +532,7 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty0 + 8 * buf, 0));   // the leader counts both CTAs
         }
-        if (__all_sync(0xffffffffu, ok && *(volatile int *)status == 0)) {
+        if (__all_sync(0xffffffffu, ok && *(volatile int *)status_word == 0)) {
             float4 *dst = reinterpret_cast<float4 *>(c + (long long)(m0 + q * 32 + lane) * N + n0 + h * HALF);
 #pragma unroll
             for (int j = 0; j < HALF / 4; j++)
@@ -542,15 +551,15 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *__restrict__ c, int N, int K, int *status)
+                 float *__restrict__ c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status);
+    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status, wait_ns, silent_producer);
 }
 
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tf32x3_2cta_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                       const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                      float *__restrict__ c, int N, int K, int *status)
+                      float *__restrict__ c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status);
+    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status, wait_ns, silent_producer);
 }

@@ -448,7 +448,12 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
         CUresult cr = dev->api->MemsetD8Async(status, 0, 4, dev->stream);
         if (cr != CUDA_SUCCESS) return sm100_fail(dev, "clearing the GEMM status word", cr);
     }
-    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &N, &K, &status };
+    /* Barrier waits inside the kernel give up after this long (default 4 s).
+     * BOOTH_SM100_GEMM_SILENT_PRODUCER=1 is the tests' fault injection: the TMA
+     * producer issues nothing, the waits run out, the kernel reports and returns. */
+    unsigned long long wait_ns = (unsigned long long)env_int("BOOTH_SM100_GEMM_WAIT_MS", 4000, 1, 60000) * 1000000ull;
+    int silent = env_int("BOOTH_SM100_GEMM_SILENT_PRODUCER", 0, 0, 1);
+    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &N, &K, &status, &wait_ns, &silent };
     if (pair)
         rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3_2CTA : SM100_K_GEMM_TF32X3_2CTA_N128,
                              2u * (unsigned)(M / 256) * (unsigned)(N / bn), 1, 1, 320, 1, 1, shmem, ga);

@@ -172,3 +172,19 @@ L.bc_free(C.byref(d), p); L.bc_device_shutdown(C.byref(d))
     assert "rc -3" in res.stdout and "rc_ok 0" in res.stdout, res.stdout + res.stderr
     assert "last dispatch: kernel 'bc_dispatch' grid 1x1x1 block 2048x1x1" in res.stderr
     assert "24 parameter bytes" in res.stderr and "buffer 'ybuf'" in res.stderr
+
+
+def test_one_process_many_devices_with_nccl(sm):
+    """examples/launch_workloads.c on two GPUs: one C99 process, a communicator over
+    both devices (sm100_comm_init_all), all-reduced sums checked against device 0
+    alone. Skipped on a single-GPU machine (the CPU coverage of the sharding rules
+    is tests/test_sharding_gloo.py)."""
+    exe = os.path.join(EXAMPLES, "launch_workloads")
+    if not os.path.exists(exe):
+        pytest.skip("build/examples/launch_workloads was not built")
+    if sm.lib().sm100_rt_device_count() < 2:
+        pytest.skip("needs two GPUs")
+    res = subprocess.run([exe, "2", "24", "20"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=300,
+                         env=dict(os.environ, LD_LIBRARY_PATH=os.path.dirname(sm.LIB_PATH), NCCL_NVLS_ENABLE="0"))
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "PASS: 2 device(s)" in res.stdout

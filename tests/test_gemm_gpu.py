@@ -1,6 +1,8 @@
 """GPU parity: fp32 GEMM (3xTF32 on tcgen05) against the CPU checker's tiled
 matmul (tests/tri_matmul_k.py called tile by tile). Relative Frobenius error
 <= 1e-5 over the compared rows."""
+import os
+
 import numpy as np
 import pytest
 
@@ -90,3 +92,38 @@ def test_gemm_full_size_sampled_rows(sm, dev, oracle_lib, size):
     assert rel_fro(got, want[rows]) <= TOL
     for p in (da, db, dc):
         dev.free(p)
+
+
+@pytest.mark.parametrize("pair", ["1", "0"])
+def test_barrier_wait_limit_reports_instead_of_hanging(sm, pair):
+    """Failure detection without a fault: with the TMA producer kept silent (a
+    host-side switch) nothing ever signals the "operands ready" barrier, so the MMA
+    issuer's and the epilogue's bounded waits run out (limit 50 ms here), the
+    kernel records which wait gave up, frees its tensor memory and returns; the
+    host reads the status at the next sync. The device stays usable."""
+    code = r"""
+import os, numpy as np, booth_b200 as sm
+d = sm.Device(0)
+M = N = 512; K = 256
+a = sm.fill_host(M * K, 5, 0, 0); b = sm.fill_host(K * N, 5, 1, 0)
+da, db, dc = d.upload(a), d.upload(b), d.alloc(M * N * 4)
+os.environ["BOOTH_SM100_GEMM_WAIT_MS"] = "50"; os.environ["BOOTH_SM100_GEMM_SILENT_PRODUCER"] = "1"
+d.gemm(dc, da, db, M, N, K)
+try:
+    d.sync(); print("no error reported")
+except sm.Sm100Error as e:
+    print("reported:", e)
+os.environ["BOOTH_SM100_GEMM_SILENT_PRODUCER"] = "0"; os.environ["BOOTH_SM100_GEMM_WAIT_MS"] = "4000"
+d.gemm(dc, da, db, M, N, K); d.sync()
+c = d.download(dc, (M, N), np.float32).astype(np.float64)
+ref = a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)
+print("after: rel", np.linalg.norm(c - ref) / np.linalg.norm(ref) < 1e-5)
+d.close()
+"""
+    import subprocess, sys
+    from conftest import ROOT
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                         text=True, timeout=120, env=dict(os.environ, BOOTH_SM100_GEMM_2CTA=pair))
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "reported:" in res.stdout and "gave up waiting on a barrier (code 2" in res.stdout + res.stderr
+    assert "after: rel True" in res.stdout
