@@ -1,5 +1,5 @@
 /* image.S -- embeds the sm_100a kernel image (a cubin built by nvcc from
- * kernels/*.cu) into libbooth_sm100.so, so the library needs no file at run time.
+ * the kernels directory) into libbooth_sm100.so, so the library needs no file at run time.
  * BOOTH_SM100_IMAGE is the path of the cubin, given by the build. */
     .section .rodata
     .balign 64

@@ -5,6 +5,7 @@
 #include "reduce.cu"
 #include "asian.cu"
 #include "tile.cu"
+#include "canonical.cu"
 #if __has_include("gemm_tf32x3.cu")
 #include "gemm_tf32x3.cu"
 #endif

@@ -504,7 +504,7 @@ CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes)
 static void snap_dispatch(sm100_dev_t *dev, const char *kernel, unsigned gx, unsigned gy, unsigned gz,
                           unsigned bx, unsigned by, unsigned bz, unsigned shmem, const void *args, unsigned args_size)
 {
-    snprintf(dev->last.kernel, sizeof dev->last.kernel, "%s", kernel && *kernel ? kernel : "?");
+    snprintf(dev->last.kernel, sizeof dev->last.kernel, "%.63s", kernel && *kernel ? kernel : "?");
     dev->last.grid[0] = gx; dev->last.grid[1] = gy; dev->last.grid[2] = gz;
     dev->last.block[0] = bx; dev->last.block[1] = by; dev->last.block[2] = bz;
     dev->last.shmem = shmem;

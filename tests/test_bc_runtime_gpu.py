@@ -188,3 +188,46 @@ def test_one_process_many_devices_with_nccl(sm):
                          env=dict(os.environ, LD_LIBRARY_PATH=os.path.dirname(sm.LIB_PATH), NCCL_NVLS_ENABLE="0"))
     assert res.returncode == 0, res.stdout + res.stderr
     assert "PASS: 2 device(s)" in res.stdout
+
+
+def test_canonical_kernels_by_name(sm, bc):
+    """matmul_general and reduce_sum (tests/canonical.cu:18-50,93-108) loaded by
+    name and launched with the reference's geometry and with an unrelated one."""
+    L, d = bc
+    M, N, K = 37, 53, 29                               # "whatever size the user fancies"
+    a = sm.fill_host(M * K, 61, 0, 0).reshape(M, K); b = sm.fill_host(K * N, 61, 1, 0).reshape(K, N)
+    want = np.zeros((M, N), np.float32)
+    for k in range(K):                                   # k ascending, product and sum rounded separately
+        want = (want + (a[:, k:k + 1] * b[k:k + 1, :]).astype(np.float32)).astype(np.float32)
+
+    class MmArgs(C.Structure):
+        _fields_ = [("C", C.c_void_p), ("A", C.c_void_p), ("B", C.c_void_p), ("M", C.c_int), ("N", C.c_int), ("K", C.c_int)]
+    k = sm.BcKernel()
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"matmul_general", C.byref(k)) == 0
+    da, db, dc = (L.bc_alloc(C.byref(d), x) for x in (M * K * 4, K * N * 4, M * N * 4))
+    L.bc_copy_h2d(C.byref(d), da, a.ctypes.data, M * K * 4); L.bc_copy_h2d(C.byref(d), db, b.ctypes.data, K * N * 4)
+    args = MmArgs(dc, da, db, M, N, K)
+    for grid, block in ((((N + 15) // 16, (M + 15) // 16, 1), (16, 16, 1)), ((2, 1, 1), (8, 4, 1))):
+        got = np.full((M, N), -1, np.float32)
+        L.bc_copy_h2d(C.byref(d), dc, got.ctypes.data, M * N * 4)
+        assert L.bc_dispatch(C.byref(d), C.byref(k), *grid, *block, C.byref(args), C.sizeof(args)) == 0
+        L.bc_copy_d2h(C.byref(d), got.ctypes.data, dc, M * N * 4)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+    L.bc_unload_kernel(C.byref(d), C.byref(k))
+
+    class RdArgs(C.Structure):
+        _fields_ = [("out", C.c_void_p), ("inp", C.c_void_p), ("n", C.c_int)]
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"reduce_sum", C.byref(k)) == 0
+    n = 100003
+    v = sm.fill_host(n, 62, 0, 1)
+    dv, do = L.bc_alloc(C.byref(d), n * 4), L.bc_alloc(C.byref(d), 4)
+    L.bc_copy_h2d(C.byref(d), dv, v.ctypes.data, n * 4)
+    for grid, block in (((64, 1, 1), (256, 1, 1)), ((3, 2, 1), (33, 1, 1))):
+        zero = np.zeros(1, np.float32)
+        L.bc_copy_h2d(C.byref(d), do, zero.ctypes.data, 4)
+        rargs = RdArgs(do, dv, n)
+        assert L.bc_dispatch(C.byref(d), C.byref(k), *grid, *block, C.byref(rargs), C.sizeof(rargs)) == 0
+        L.bc_copy_d2h(C.byref(d), zero.ctypes.data, do, 4)
+        assert abs(float(zero[0]) - float(v.astype(np.float64).sum())) <= 2e-5 * n * 0.5
+    for p in (da, db, dc, dv, do):
+        L.bc_free(C.byref(d), p)
