@@ -8,9 +8,13 @@
 //     a.b  ~=  a_lo.b_hi + a_hi.b_lo + a_hi.b_hi        (a_lo.b_lo ~ 2^-22 dropped)
 // which keeps the result within ~1e-6 of an fp32 GEMM.
 //
+// Any positive M, N, K: the split kernels write the planes padded with zeros to
+// whole tiles (Mp, Np, Kp), the contraction runs on the padded planes (K here is
+// Kp), and the epilogue stores only the M x N that exist.
+//
 // Three kernels:
-//   gemm_split_a    A[M,K]  -> A_hi, A_lo [M,K]            (elementwise, streaming)
-//   gemm_split_bt   B[K,N]  -> Bt_hi, Bt_lo [N,K]          (split + transpose through
+//   gemm_split_a    A[M,K]  -> A_hi, A_lo [Mp,Kp]          (elementwise, streaming)
+//   gemm_split_bt   B[K,N]  -> Bt_hi, Bt_lo [Np,Kp]        (split + transpose through
 //                   shared memory, so both MMA operands are K-major)
 //   gemm_tf32x3     one 128 x BN tile of C per CTA:
 //       warp 0, one lane : TMA producer. cp.async.bulk.tensor (128-byte swizzle, no
@@ -131,13 +135,28 @@ __device__ __forceinline__ float to_tf32(float x)
 
 }  // namespace gemm
 
-// hi[i] = tf32(a[i]), lo[i] = tf32(a[i] - hi[i]); n is a multiple of 4.
-extern "C" __global__ void gemm_split_a(const float4 *__restrict__ a, float4 *__restrict__ hi,
-                                        float4 *__restrict__ lo, long long n4)
+// A[M,K] row-major -> hi/lo planes [Mp,Kp] (Mp >= M, Kp >= K, Kp % 4 == 0), zero in
+// the padding: hi = tf32(a), lo = tf32(a - hi). Without padding and with K % 4 == 0
+// the planes are walked as one flat array of 16-byte chunks.
+extern "C" __global__ void gemm_split_a(const float *__restrict__ a, float4 *__restrict__ hi,
+                                        float4 *__restrict__ lo, int M, int K, int Mp, int Kp)
 {
     const long long T = (long long)gridDim.x * blockDim.x;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += T) {
-        const float4 v = __ldcs(a + i);
+    const long long kp4 = Kp >> 2, total = (long long)Mp * kp4;
+    const bool flat = M == Mp && K == Kp && (((uintptr_t)a) & 15) == 0;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += T) {
+        float4 v;
+        if (flat) {
+            v = __ldcs(reinterpret_cast<const float4 *>(a) + i);
+        } else {
+            const long long row = i / kp4;
+            const int k = (int)(i - row * kp4) << 2;
+            const float *src = a + row * K + k;
+            v.x = (row < M && k + 0 < K) ? src[0] : 0.0f;
+            v.y = (row < M && k + 1 < K) ? src[1] : 0.0f;
+            v.z = (row < M && k + 2 < K) ? src[2] : 0.0f;
+            v.w = (row < M && k + 3 < K) ? src[3] : 0.0f;
+        }
         float4 h, l;
         h.x = gemm::to_tf32(v.x); l.x = gemm::to_tf32(v.x - h.x);
         h.y = gemm::to_tf32(v.y); l.y = gemm::to_tf32(v.y - h.y);
@@ -148,24 +167,48 @@ extern "C" __global__ void gemm_split_a(const float4 *__restrict__ a, float4 *__
     }
 }
 
-// B[K,N] row-major -> hi/lo planes of B^T, [N,K] row-major. 32x32 tiles through
-// shared memory (padded against bank conflicts); block (32,8), grid (N/32, K/32).
+// B[K,N] row-major -> hi/lo planes of B^T, [Np,Kp] row-major, zero in the padding.
+// 32x32 tiles through shared memory (padded against bank conflicts); block (32,8),
+// grid (Np/32, Kp/32).
 extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__restrict__ hi,
-                                         float *__restrict__ lo, int K, int N)
+                                         float *__restrict__ lo, int K, int N, int Kp)
 {
     __shared__ float tile[32][33];
     const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
-    for (int r = threadIdx.y; r < 32; r += 8)
-        tile[r][threadIdx.x] = b[(long long)(k0 + r) * N + n0 + threadIdx.x];
+    for (int r = threadIdx.y; r < 32; r += 8) {
+        const int k = k0 + r, n = n0 + threadIdx.x;
+        tile[r][threadIdx.x] = (k < K && n < N) ? b[(long long)k * N + n] : 0.0f;
+    }
     __syncthreads();
     for (int r = threadIdx.y; r < 32; r += 8) {
         const float v = tile[threadIdx.x][r];
         const float h = gemm::to_tf32(v);
-        const long long o = (long long)(n0 + r) * K + k0 + threadIdx.x;
+        const long long o = (long long)(n0 + r) * Kp + k0 + threadIdx.x;
         hi[o] = h;
         lo[o] = gemm::to_tf32(v - h);
     }
 }
+
+namespace gemm {
+// One thread's HALF consecutive columns of one row of C, from its register sums.
+// Whole 16-byte stores when the row segment lies inside C and is aligned, masked
+// scalar stores at a ragged right edge; rows beyond M are padding and are dropped.
+template <int HALF>
+__device__ __forceinline__ void store_row(float *__restrict__ c, const float (&acc)[HALF], int row, int col0, int M, int N)
+{
+    if (row >= M) return;
+    float *dst = c + (long long)row * N + col0;
+    if (col0 + HALF <= N && (N & 3) == 0 && (((uintptr_t)c) & 15) == 0) {
+#pragma unroll
+        for (int j = 0; j < HALF / 4; j++)
+            reinterpret_cast<float4 *>(dst)[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+    } else {
+#pragma unroll
+        for (int j = 0; j < HALF; j++)
+            if (col0 + j < N) dst[j] = acc[j];
+    }
+}
+}  // namespace gemm
 
 // One 128 x BN tile of C per CTA; grid (N/BN, M/128), 320 threads,
 // dynamic shared memory = STAGES * (2*128 + 2*BN) * 128 bytes + 1024 (alignment).
@@ -180,7 +223,7 @@ extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__r
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUtensorMap *map_a_lo,
                                           const CUtensorMap *map_b_hi, const CUtensorMap *map_b_lo,
-                                          float *__restrict__ c, int N, int K, int *status_word,
+                                          float *__restrict__ c, int M, int N, int K, int *status_word,
                                           unsigned long long wait_ns, int silent_producer)
 {
     using namespace gemm;
@@ -299,10 +342,7 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
                 asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(acc_empty0 + 8 * buf) : "memory");
         }
         if (__all_sync(0xffffffffu, ok && *(volatile int *)status_word == 0)) {
-            float4 *dst = reinterpret_cast<float4 *>(c + (long long)(m0 + q * 32 + lane) * N + n0 + h * HALF);
-#pragma unroll
-            for (int j = 0; j < HALF / 4; j++)
-                dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            store_row<HALF>(c, acc, m0 + q * 32 + lane, n0 + h * HALF, M, N);
         } else {
             // A wait ran out: give copies that may still be in flight time to
             // land before the shared memory is released.
@@ -318,17 +358,19 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
 extern "C" __global__ void __launch_bounds__(320, 1)
 gemm_tf32x3(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
             const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-            float *c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
+            float *c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_tile<256, 2>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status, wait_ns, silent_producer);
+    (void)Np;
+    gemm_tile<256, 2>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, M, N, K, status, wait_ns, silent_producer);
 }
 
 extern "C" __global__ void __launch_bounds__(320, 1)
 gemm_tf32x3_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
+                 float *c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, N, K, status, wait_ns, silent_producer);
+    (void)Np;
+    gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, M, N, K, status, wait_ns, silent_producer);
 }
 
 
@@ -408,7 +450,7 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int bn)     // M = 256 ac
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, const CUtensorMap &map_a_lo,
                                                const CUtensorMap &map_b_hi, const CUtensorMap &map_b_lo,
-                                               float *__restrict__ c, int N, int K, int *status_word,
+                                               float *__restrict__ c, int M, int N, int Np, int K, int *status_word,
                                                unsigned long long wait_ns, int silent_producer)
 {
     using namespace gemm;
@@ -430,7 +472,7 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
     const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
     const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tiles_n = N / BN;
+    const int tiles_n = Np / BN;
     const int tile = blockIdx.x >> 1;
     const int m0 = (tile / tiles_n) * 256 + (int)rank * BM;             // this CTA's rows of A and C
     const int n0 = (tile % tiles_n) * BN;
@@ -533,10 +575,7 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty0 + 8 * buf, 0));   // the leader counts both CTAs
         }
         if (__all_sync(0xffffffffu, ok && *(volatile int *)status_word == 0)) {
-            float4 *dst = reinterpret_cast<float4 *>(c + (long long)(m0 + q * 32 + lane) * N + n0 + h * HALF);
-#pragma unroll
-            for (int j = 0; j < HALF / 4; j++)
-                dst[j] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
+            store_row<HALF>(c, acc, m0 + q * 32 + lane, n0 + h * HALF, M, N);
         } else {
             for (int i = 0; i < 64; i++) __nanosleep(4000);
         }
@@ -551,15 +590,15 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *__restrict__ c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
+                 float *__restrict__ c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status, wait_ns, silent_producer);
+    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, status, wait_ns, silent_producer);
 }
 
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tf32x3_2cta_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                       const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                      float *__restrict__ c, int N, int K, int *status, unsigned long long wait_ns, int silent_producer)
+                      float *__restrict__ c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, N, K, status, wait_ns, silent_producer);
+    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, status, wait_ns, silent_producer);
 }

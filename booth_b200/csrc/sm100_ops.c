@@ -399,34 +399,39 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
 {
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
-    if (!c || !a || !b || M <= 0 || N <= 0 || K <= 0 || (M % 128) || (N % 256) || (K % 32) || ((a | b | c) & 15))
-        return bad_arg(dev, "booth_sm100_gemm: need M % 128 == 0, N % 256 == 0, K % 32 == 0, 16-byte aligned pointers");
-    /* Two-CTA clusters whenever M allows; BOOTH_SM100_GEMM_2CTA=0 forces the one-CTA form. */
-    const int pair = (M % 256 == 0) && env_int("BOOTH_SM100_GEMM_2CTA", 1, 0, 1);
+    if (!c || !a || !b || M <= 0 || N <= 0 || K <= 0 || ((a | b | c) & 3) ||
+        (long long)M + 255 > INT_MAX || (long long)N + 255 > INT_MAX || (long long)K + 31 > INT_MAX)
+        return bad_arg(dev, "booth_sm100_gemm: need positive M, N, K and 4-byte aligned pointers");
     /* 256-wide tiles. The 128-wide forms (BOOTH_SM100_GEMM_BN=128) fill the last
      * wave of mid-sized problems better but measured slower everywhere (4096^3:
      * 184 against 226 TFLOP/s with CTA pairs): the narrower MMA re-reads A twice as
      * often from shared memory. */
     const int bn = env_int("BOOTH_SM100_GEMM_BN", 256, 128, 256) == 128 ? 128 : 256;
-    const size_t a_bytes = (size_t)M * K * 4, b_bytes = (size_t)N * K * 4;
+    /* Padded extents: whole tiles. CTA pairs (256-row tiles) when the rows come
+     * out even, or when M is large enough that rounding up to 256 wastes little;
+     * BOOTH_SM100_GEMM_2CTA=0 forces the one-CTA form. */
+    int Mp = (M + 127) / 128 * 128;
+    int pair = env_int("BOOTH_SM100_GEMM_2CTA", 1, 0, 1) && (Mp % 256 == 0 || M >= 2048);
+    if (pair) Mp = (M + 255) / 256 * 256;
+    const int Np = (N + 255) / 256 * 256, Kp = (K + 31) / 32 * 32;
+    const size_t a_bytes = (size_t)Mp * Kp * 4, b_bytes = (size_t)Np * Kp * 4;
     CUdeviceptr ws = sm100_gemm_ws(dev, 2 * a_bytes + 2 * b_bytes);
     if (!ws) return SM100_ERR_CUDA;
     CUdeviceptr a_hi = ws, a_lo = ws + a_bytes, b_hi = ws + 2 * a_bytes, b_lo = b_hi + b_bytes;
 
-    /* 1. split A, split + transpose B */
-    long long n4 = (long long)M * K / 4;
-    void *sa[] = { &a, &a_hi, &a_lo, &n4 };
+    /* 1. split A, split + transpose B (both write zeros into the padding) */
+    void *sa[] = { &a, &a_hi, &a_lo, &M, &K, &Mp, &Kp };
     if ((rc = sm100_launch_k(dev, SM100_K_GEMM_SPLIT_A, (unsigned)dev->sm_count * 8, 256, 0, sa)) != SM100_OK) return rc;
-    void *sb[] = { &b, &b_hi, &b_lo, &K, &N };
-    if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(N / 32), (unsigned)(K / 32), 1, 32, 8, 1, 0, sb)) != SM100_OK)
+    void *sb[] = { &b, &b_hi, &b_lo, &K, &N, &Kp };
+    if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(Np / 32), (unsigned)(Kp / 32), 1, 32, 8, 1, 0, sb)) != SM100_OK)
         return rc;
 
     /* 2. the tiled contraction */
     CUtensorMap maps[4];
-    if ((rc = tmap_2d(dev, &maps[0], a_hi, M, K, 128)) != SM100_OK) return rc;
-    if ((rc = tmap_2d(dev, &maps[1], a_lo, M, K, 128)) != SM100_OK) return rc;
-    if ((rc = tmap_2d(dev, &maps[2], b_hi, N, K, pair ? bn / 2 : bn)) != SM100_OK) return rc;
-    if ((rc = tmap_2d(dev, &maps[3], b_lo, N, K, pair ? bn / 2 : bn)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[0], a_hi, Mp, Kp, 128)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[1], a_lo, Mp, Kp, 128)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[2], b_hi, Np, Kp, pair ? bn / 2 : bn)) != SM100_OK) return rc;
+    if ((rc = tmap_2d(dev, &maps[3], b_lo, Np, Kp, pair ? bn / 2 : bn)) != SM100_OK) return rc;
     const unsigned shmem = 197632;     /* stages * stage bytes + 1024: 2 x 96 KB, 3 x 64 KB or 4 x 48 KB, the same for every form */
     if (!dev->gemm_smem_set) {
         CUresult cr = dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_TF32X3],
@@ -453,13 +458,13 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
      * producer issues nothing, the waits run out, the kernel reports and returns. */
     unsigned long long wait_ns = (unsigned long long)env_int("BOOTH_SM100_GEMM_WAIT_MS", 4000, 1, 60000) * 1000000ull;
     int silent = env_int("BOOTH_SM100_GEMM_SILENT_PRODUCER", 0, 0, 1);
-    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &N, &K, &status, &wait_ns, &silent };
+    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &M, &N, &Np, &Kp, &status, &wait_ns, &silent };
     if (pair)
         rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3_2CTA : SM100_K_GEMM_TF32X3_2CTA_N128,
-                             2u * (unsigned)(M / 256) * (unsigned)(N / bn), 1, 1, 320, 1, 1, shmem, ga);
+                             2u * (unsigned)(Mp / 256) * (unsigned)(Np / bn), 1, 1, 320, 1, 1, shmem, ga);
     else
         rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3 : SM100_K_GEMM_TF32X3_N128,
-                             (unsigned)(N / bn), (unsigned)(M / 128), 1, 320, 1, 1, shmem, ga);
+                             (unsigned)(Np / bn), (unsigned)(Mp / 128), 1, 320, 1, 1, shmem, ga);
     if (rc == SM100_OK) dev->gemm_pending = 1;
     return rc;
 }

@@ -185,8 +185,9 @@ int  booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
  * overlap on the GPU. This entry point has no counterpart in the reference. */
 int  booth_sm100_reduce_f32_noalloc(sm100_ptr_t in, long long n, sm100_ptr_t out, void *stream);
 /* C[M,N] = A[M,K] * B[K,N], row-major fp32, 3xTF32 on the tensor cores:
- * the tests/tri_matmul_k.py:8-23 / tests/canonical.cu:18-50 contraction.
- * M % 128 == 0, N % 256 == 0, K % 32 == 0. */
+ * the tests/tri_matmul_k.py:8-23 / tests/canonical.cu:18-50 contraction. Any
+ * positive M, N, K (operands are padded to whole tiles in the workspace);
+ * multiples of 256 / 256 / 32 waste nothing. */
 int  booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a,
                       sm100_ptr_t b, int M, int N, int K);
 

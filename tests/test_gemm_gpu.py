@@ -65,11 +65,40 @@ def test_gemm_layout_identity_and_one_hot(sm, dev):
 
 def test_gemm_argument_errors(sm, dev):
     p = dev.alloc(1 << 20)
-    for M, N, K in ((100, 256, 32), (128, 200, 32), (128, 256, 30), (0, 256, 32)):
+    for M, N, K in ((0, 256, 32), (128, -1, 32), (128, 256, 0)):
         with pytest.raises(sm.Sm100Error) as e:
             dev.gemm(p, p, p, M, N, K)
         assert e.value.code == sm.ERR_ARG
+    with pytest.raises(sm.Sm100Error):
+        dev.gemm(0, p, p, 128, 256, 32)
     dev.free(p)
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (4, 4, 4), (100, 200, 50), (129, 257, 33), (128, 256, 30),
+                                   (300, 1000, 514), (1000, 1000, 1000), (2500, 260, 64)])
+def test_gemm_any_size(sm, dev, oracle_lib, M, N, K):
+    """Sizes that are not whole tiles: the planes are zero-padded in the workspace
+    and only the M x N that exist are stored (the memory after C stays untouched).
+    The CPU checker's 4x4x2 tiles need M, N % 4 == 0 and K % 2 == 0; other sizes are
+    checked against a double-precision product."""
+    a, b = inputs(sm, M, N, K, seed=77)
+    da, db = dev.upload(a), dev.upload(b)
+    guard = 64
+    dc = dev.alloc((M * N + guard) * 4)
+    sentinel = np.full(M * N + guard, -7.5, np.float32)
+    dev.h2d(dc, sentinel)
+    dev.gemm(dc, da, db, M, N, K)
+    dev.sync()
+    raw = dev.download(dc, M * N + guard, np.float32)
+    got = raw[:M * N].reshape(M, N)
+    assert np.all(raw[M * N:] == np.float32(-7.5))
+    if M % 4 == 0 and N % 4 == 0 and K % 2 == 0:
+        want = oracle_lib.matmul(a, b)
+    else:
+        want = (a.astype(np.float64) @ b.astype(np.float64))
+    assert rel_fro(got, want) <= TOL
+    for p in (da, db, dc):
+        dev.free(p)
 
 
 @pytest.mark.parametrize("size", [4096, 8192])
