@@ -295,7 +295,7 @@ def run_ours(args):
                     comm.allreduce_sum(out, 4, sm.F64)
             mc_sampler = ClockSampler(ranks.local)
             mc_sampler.start()
-            t = timed(dev, ranks, W if not precise else 1, ksteps, mc_step) / ksteps
+            t = timed(dev, ranks, W, ksteps, mc_step) / ksteps
             mc_clocks = mc_sampler.stop()
             s = dev.download(out, 4, np.float64)
             tot = npaths * G
