@@ -189,10 +189,36 @@ extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__r
     }
 }
 
+// Zeroes the 256 x 256 tiles [tile_from, tile_to) of C (tile t covers rows
+// (t / tiles_n) * 256.. and columns (t % tiles_n) * 256..), clipped to M x N: the
+// tiles two clusters will add their halves of K into. One block per tile.
+extern "C" __global__ void gemm_zero_tiles(float *__restrict__ c, int M, int N, int tiles_n, int tile_from)
+{
+    const int t = tile_from + blockIdx.x;
+    const int r0 = (t / tiles_n) * 256, c0 = (t % tiles_n) * 256;
+    for (int i = threadIdx.x; i < 256 * 256; i += blockDim.x) {
+        const int r = r0 + (i >> 8), col = c0 + (i & 255);
+        if (r < M && col < N) c[(long long)r * N + col] = 0.0f;
+    }
+}
+
 namespace gemm {
 // One thread's HALF consecutive columns of one row of C, from its register sums.
 // Whole 16-byte stores when the row segment lies inside C and is aligned, masked
 // scalar stores at a ragged right edge; rows beyond M are padding and are dropped.
+// add_row is the same for a tile whose K range is shared by two clusters: C was
+// zeroed beforehand and both halves are added with fp32 atomics (two addends on
+// zero: the sum does not depend on their order).
+template <int HALF>
+__device__ __forceinline__ void add_row(float *__restrict__ c, const float (&acc)[HALF], int row, int col0, int M, int N)
+{
+    if (row >= M) return;
+    float *dst = c + (long long)row * N + col0;
+#pragma unroll
+    for (int j = 0; j < HALF; j++)
+        if (col0 + j < N) atomicAdd(dst + j, acc[j]);
+}
+
 template <int HALF>
 __device__ __forceinline__ void store_row(float *__restrict__ c, const float (&acc)[HALF], int row, int col0, int M, int N)
 {
@@ -358,18 +384,18 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
 extern "C" __global__ void __launch_bounds__(320, 1)
 gemm_tf32x3(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
             const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-            float *c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
+            float *c, int M, int N, int Np, int K, int split_from, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    (void)Np;
+    (void)Np; (void)split_from;
     gemm_tile<256, 2>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, M, N, K, status, wait_ns, silent_producer);
 }
 
 extern "C" __global__ void __launch_bounds__(320, 1)
 gemm_tf32x3_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
+                 float *c, int M, int N, int Np, int K, int split_from, int *status, unsigned long long wait_ns, int silent_producer)
 {
-    (void)Np;
+    (void)Np; (void)split_from;
     gemm_tile<128, 3>(&map_a_hi, &map_a_lo, &map_b_hi, &map_b_lo, c, M, N, K, status, wait_ns, silent_producer);
 }
 
@@ -450,7 +476,7 @@ __host__ __device__ constexpr uint32_t instr_desc_pair(int bn)     // M = 256 ac
 template <int BN, int STAGES>
 __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, const CUtensorMap &map_a_lo,
                                                const CUtensorMap &map_b_hi, const CUtensorMap &map_b_lo,
-                                               float *__restrict__ c, int M, int N, int Np, int K, int *status_word,
+                                               float *__restrict__ c, int M, int N, int Np, int K, int split_from, int *status_word,
                                                unsigned long long wait_ns, int silent_producer)
 {
     using namespace gemm;
@@ -473,11 +499,18 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
     const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tiles_n = Np / BN;
-    const int tile = blockIdx.x >> 1;
+    // Clusters [0, split_from) compute one tile each over all of K. From
+    // split_from on, two consecutive clusters share a tile and take half of K each
+    // (the host uses this for the tiles of a short last wave).
+    const int cl = blockIdx.x >> 1;
+    const bool shared_tile = cl >= split_from;
+    const int tile = shared_tile ? split_from + ((cl - split_from) >> 1) : cl;
+    const int kpart = shared_tile ? ((cl - split_from) & 1) : 0;
     const int m0 = (tile / tiles_n) * 256 + (int)rank * BM;             // this CTA's rows of A and C
     const int n0 = (tile % tiles_n) * BN;
     const int nb0 = n0 + (int)rank * HALF_N;                            // this CTA's rows of B^T
-    const int nkb = K / BK;
+    const int nkb = shared_tile ? (K / BK) / 2 : K / BK;             // K blocks this cluster covers
+    const int kb0 = kpart * nkb;                                     // ... starting here
     const int nchunk = (nkb + CHUNK_KB - 1) / CHUNK_KB;
 
     if (threadIdx.x == 0) {
@@ -506,10 +539,10 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
                 const uint32_t st = smem0 + (uint32_t)s * STAGE_BYTES;
                 const uint32_t full_leader = map_to_cta(full0 + 8 * s, 0);
                 if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
-                tma_load_2d_pair(st, &map_a_hi, full_leader, kb * BK, m0);
-                tma_load_2d_pair(st + A_BYTES, &map_a_lo, full_leader, kb * BK, m0);
-                tma_load_2d_pair(st + 2 * A_BYTES, &map_b_hi, full_leader, kb * BK, nb0);
-                tma_load_2d_pair(st + 2 * A_BYTES + B_BYTES, &map_b_lo, full_leader, kb * BK, nb0);
+                tma_load_2d_pair(st, &map_a_hi, full_leader, (kb0 + kb) * BK, m0);
+                tma_load_2d_pair(st + A_BYTES, &map_a_lo, full_leader, (kb0 + kb) * BK, m0);
+                tma_load_2d_pair(st + 2 * A_BYTES, &map_b_hi, full_leader, (kb0 + kb) * BK, nb0);
+                tma_load_2d_pair(st + 2 * A_BYTES + B_BYTES, &map_b_lo, full_leader, (kb0 + kb) * BK, nb0);
             }
         }
         __syncwarp();
@@ -575,7 +608,8 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
             if (lane == 0) mbar_arrive_cluster(map_to_cta(acc_empty0 + 8 * buf, 0));   // the leader counts both CTAs
         }
         if (__all_sync(0xffffffffu, ok && *(volatile int *)status_word == 0)) {
-            store_row<HALF>(c, acc, m0 + q * 32 + lane, n0 + h * HALF, M, N);
+            if (shared_tile) add_row<HALF>(c, acc, m0 + q * 32 + lane, n0 + h * HALF, M, N);
+            else store_row<HALF>(c, acc, m0 + q * 32 + lane, n0 + h * HALF, M, N);
         } else {
             for (int i = 0; i < 64; i++) __nanosleep(4000);
         }
@@ -590,15 +624,17 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tf32x3_2cta(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                 float *__restrict__ c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
+                 float *__restrict__ c, int M, int N, int Np, int K, int split_from, int *status, unsigned long long wait_ns,
+                 int silent_producer)
 {
-    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, status, wait_ns, silent_producer);
+    gemm_pair_tile<256, 3>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, split_from, status, wait_ns, silent_producer);
 }
 
 extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(320, 1)
 gemm_tf32x3_2cta_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
                       const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                      float *__restrict__ c, int M, int N, int Np, int K, int *status, unsigned long long wait_ns, int silent_producer)
+                      float *__restrict__ c, int M, int N, int Np, int K, int split_from, int *status, unsigned long long wait_ns,
+                 int silent_producer)
 {
-    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, status, wait_ns, silent_producer);
+    gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, split_from, status, wait_ns, silent_producer);
 }

@@ -70,7 +70,7 @@ enum {
     SM100_K_REDUCE_I32, SM100_K_REDUCE_F32,
     SM100_K_ASIAN_MC, SM100_K_ASIAN_MC_PRECISE,
     SM100_K_ASIAN_PATHS, SM100_K_ASIAN_PATHS_PRECISE,
-    SM100_K_GEMM_SPLIT_A, SM100_K_GEMM_SPLIT_BT, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128,
+    SM100_K_GEMM_SPLIT_A, SM100_K_GEMM_SPLIT_BT, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_ZERO_TILES,
     SM100_K_COUNT
 };
 

@@ -413,7 +413,7 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     int Mp = (M + 127) / 128 * 128;
     int pair = env_int("BOOTH_SM100_GEMM_2CTA", 1, 0, 1) && (Mp % 256 == 0 || M >= 2048);
     if (pair) Mp = (M + 255) / 256 * 256;
-    const int Np = (N + 255) / 256 * 256, Kp = (K + 31) / 32 * 32;
+    int Np = (N + 255) / 256 * 256, Kp = (K + 31) / 32 * 32;
     const size_t a_bytes = (size_t)Mp * Kp * 4, b_bytes = (size_t)Np * Kp * 4;
     CUdeviceptr ws = sm100_gemm_ws(dev, 2 * a_bytes + 2 * b_bytes);
     if (!ws) return SM100_ERR_CUDA;
@@ -458,10 +458,25 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
      * producer issues nothing, the waits run out, the kernel reports and returns. */
     unsigned long long wait_ns = (unsigned long long)env_int("BOOTH_SM100_GEMM_WAIT_MS", 4000, 1, 60000) * 1000000ull;
     int silent = env_int("BOOTH_SM100_GEMM_SILENT_PRODUCER", 0, 0, 1);
-    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &M, &N, &Np, &Kp, &status, &wait_ns, &silent };
+    /* A short last wave: when the tiles left over after the full waves occupy at
+     * most half of the SM pairs, each of them is shared by two clusters that take
+     * half of K each and add into a zeroed C (4096^3: 256 tiles on 74 pairs are 3
+     * waves + 34 tiles; sharing them turns the fourth wave into half a wave).
+     * BOOTH_SM100_GEMM_SPLIT_TAIL=0 disables it. */
+    int tiles = pair && bn == 256 ? (Mp / 256) * (Np / 256) : 0, split_from = tiles, shared = 0;
+    if (tiles && env_int("BOOTH_SM100_GEMM_SPLIT_TAIL", 1, 0, 1)) {
+        const int slots = dev->sm_count / 2, rem = slots > 0 ? tiles % slots : 0;
+        if (rem > 0 && 2 * rem <= slots && (Kp / 32) % 2 == 0 && Kp >= 1024) { shared = rem; split_from = tiles - rem; }
+    }
+    if (shared) {
+        int tiles_n = Np / 256;
+        void *za[] = { &c, &M, &N, &tiles_n, &split_from };
+        if ((rc = sm100_launch_k(dev, SM100_K_GEMM_ZERO_TILES, (unsigned)shared, 256, 0, za)) != SM100_OK) return rc;
+    }
+    void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &M, &N, &Np, &Kp, &split_from, &status, &wait_ns, &silent };
     if (pair)
         rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3_2CTA : SM100_K_GEMM_TF32X3_2CTA_N128,
-                             2u * (unsigned)(Mp / 256) * (unsigned)(Np / bn), 1, 1, 320, 1, 1, shmem, ga);
+                             2u * ((unsigned)(Mp / 256) * (unsigned)(Np / bn) + (unsigned)shared), 1, 1, 320, 1, 1, shmem, ga);
     else
         rc = sm100_launch_k3(dev, bn == 256 ? SM100_K_GEMM_TF32X3 : SM100_K_GEMM_TF32X3_N128,
                              (unsigned)(Np / bn), (unsigned)(Mp / 128), 1, 320, 1, 1, shmem, ga);
