@@ -189,13 +189,32 @@ extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__r
     }
 }
 
-// Zeroes the 256 x 256 tiles [tile_from, tile_to) of C (tile t covers rows
-// (t / tiles_n) * 256.. and columns (t % tiles_n) * 256..), clipped to M x N: the
-// tiles two clusters will add their halves of K into. One block per tile.
+namespace gemm {
+// Pair-tile index -> (tile row, tile column). Tiles are numbered in groups of
+// eight tile rows, column by column inside a group, so the ~74 tiles that run at
+// the same time form a block about 8 tall and 9 wide and share their A and B
+// panels through L2 (a row-major numbering would touch every panel of B in
+// every wave).
+__device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tiles_n, int &tm, int &tn)
+{
+    constexpr int GROUP_M = 8;
+    const int per_group = GROUP_M * tiles_n;
+    const int g = tile / per_group, first_m = g * GROUP_M;
+    const int rows = min(tiles_m - first_m, GROUP_M);
+    const int in_group = tile - g * per_group;
+    tm = first_m + in_group % rows;
+    tn = in_group / rows;
+}
+}  // namespace gemm
+
+// Zeroes the 256 x 256 tiles of C numbered tile_from, tile_from + 1, ... (one
+// block per tile, numbering of pair_tile_coords), clipped to M x N: the tiles two
+// clusters will add their halves of K into.
 extern "C" __global__ void gemm_zero_tiles(float *__restrict__ c, int M, int N, int tiles_n, int tile_from)
 {
-    const int t = tile_from + blockIdx.x;
-    const int r0 = (t / tiles_n) * 256, c0 = (t % tiles_n) * 256;
+    int tm, tn;
+    gemm::pair_tile_coords(tile_from + blockIdx.x, (M + 255) / 256, tiles_n, tm, tn);
+    const int r0 = tm * 256, c0 = tn * 256;
     for (int i = threadIdx.x; i < 256 * 256; i += blockDim.x) {
         const int r = r0 + (i >> 8), col = c0 + (i & 255);
         if (r < M && col < N) c[(long long)r * N + col] = 0.0f;
@@ -506,8 +525,10 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
     const bool shared_tile = cl >= split_from;
     const int tile = shared_tile ? split_from + ((cl - split_from) >> 1) : cl;
     const int kpart = shared_tile ? ((cl - split_from) & 1) : 0;
-    const int m0 = (tile / tiles_n) * 256 + (int)rank * BM;             // this CTA's rows of A and C
-    const int n0 = (tile % tiles_n) * BN;
+    int tm, tn;
+    pair_tile_coords(tile, (M + 255) / 256, tiles_n, tm, tn);
+    const int m0 = tm * 256 + (int)rank * BM;                           // this CTA's rows of A and C
+    const int n0 = tn * BN;
     const int nb0 = n0 + (int)rank * HALF_N;                            // this CTA's rows of B^T
     const int nkb = shared_tile ? (K / BK) / 2 : K / BK;             // K blocks this cluster covers
     const int kb0 = kpart * nkb;                                     // ... starting here
