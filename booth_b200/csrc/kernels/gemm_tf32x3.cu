@@ -168,24 +168,48 @@ extern "C" __global__ void gemm_split_a(const float *__restrict__ a, float4 *__r
 }
 
 // B[K,N] row-major -> hi/lo planes of B^T, [Np,Kp] row-major, zero in the padding.
-// 32x32 tiles through shared memory (padded against bank conflicts); block (32,8),
-// grid (Np/32, Kp/32).
-extern "C" __global__ void gemm_split_bt(const float *__restrict__ b, float *__restrict__ hi,
-                                         float *__restrict__ lo, int K, int N, int Kp)
+// 64x64 tiles through shared memory (padded against bank conflicts), 256 threads,
+// grid (Np/64, ceil(Kp/64)): rows of B are read in 256-byte runs (16-byte loads
+// when N and the pointer allow), rows of B^T written in 256-byte runs of 16-byte
+// stores.
+extern "C" __global__ void __launch_bounds__(256)
+gemm_split_bt(const float *__restrict__ b, float *__restrict__ hi, float *__restrict__ lo, int K, int N, int Kp)
 {
-    __shared__ float tile[32][33];
-    const int n0 = blockIdx.x * 32, k0 = blockIdx.y * 32;
-    for (int r = threadIdx.y; r < 32; r += 8) {
-        const int k = k0 + r, n = n0 + threadIdx.x;
-        tile[r][threadIdx.x] = (k < K && n < N) ? b[(long long)k * N + n] : 0.0f;
+    __shared__ float tile[64][65];            // [k][n]
+    const int n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+    const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // 16 x 16
+    const bool vec = (N & 3) == 0 && (((uintptr_t)b) & 15) == 0;
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const int k = k0 + ty + 16 * p, n = n0 + 4 * tx;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (k < K) {
+            const float *src = b + (long long)k * N + n;
+            if (vec && n + 3 < N) v = __ldcs(reinterpret_cast<const float4 *>(src));
+            else {
+                if (n + 0 < N) v.x = src[0];
+                if (n + 1 < N) v.y = src[1];
+                if (n + 2 < N) v.z = src[2];
+                if (n + 3 < N) v.w = src[3];
+            }
+        }
+        float *t = &tile[ty + 16 * p][4 * tx];
+        t[0] = v.x; t[1] = v.y; t[2] = v.z; t[3] = v.w;
     }
     __syncthreads();
-    for (int r = threadIdx.y; r < 32; r += 8) {
-        const float v = tile[threadIdx.x][r];
-        const float h = gemm::to_tf32(v);
-        const long long o = (long long)(n0 + r) * Kp + k0 + threadIdx.x;
-        hi[o] = h;
-        lo[o] = gemm::to_tf32(v - h);
+#pragma unroll
+    for (int p = 0; p < 4; p++) {
+        const int nl = ty + 16 * p, k = k0 + 4 * tx;                 // one row of B^T, four consecutive k
+        if (k >= Kp) continue;
+        float4 h, l;
+        const float v0 = tile[4 * tx + 0][nl], v1 = tile[4 * tx + 1][nl], v2 = tile[4 * tx + 2][nl], v3 = tile[4 * tx + 3][nl];
+        h.x = gemm::to_tf32(v0); l.x = gemm::to_tf32(v0 - h.x);
+        h.y = gemm::to_tf32(v1); l.y = gemm::to_tf32(v1 - h.y);
+        h.z = gemm::to_tf32(v2); l.z = gemm::to_tf32(v2 - h.z);
+        h.w = gemm::to_tf32(v3); l.w = gemm::to_tf32(v3 - h.w);
+        const long long o = (long long)(n0 + nl) * Kp + k;
+        *reinterpret_cast<float4 *>(hi + o) = h;
+        *reinterpret_cast<float4 *>(lo + o) = l;
     }
 }
 

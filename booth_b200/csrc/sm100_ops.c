@@ -423,7 +423,7 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     void *sa[] = { &a, &a_hi, &a_lo, &M, &K, &Mp, &Kp };
     if ((rc = sm100_launch_k(dev, SM100_K_GEMM_SPLIT_A, (unsigned)dev->sm_count * 8, 256, 0, sa)) != SM100_OK) return rc;
     void *sb[] = { &b, &b_hi, &b_lo, &K, &N, &Kp };
-    if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(Np / 32), (unsigned)(Kp / 32), 1, 32, 8, 1, 0, sb)) != SM100_OK)
+    if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(Np / 64), (unsigned)((Kp + 63) / 64), 1, 256, 1, 1, 0, sb)) != SM100_OK)
         return rc;
 
     /* 2. the tiled contraction */
