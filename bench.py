@@ -328,6 +328,12 @@ def run_ours(args):
     }
     if ranks.rank == 0 and G == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline_saxpy(args.cpu_seconds)
+        if workloads:
+            others = cpu_baselines_other()
+            for wl in workloads:
+                for fam, base in others.items():
+                    if wl["name"].startswith(fam if fam != "asian" else "asian_mc") and "value" in wl:
+                        wl["cpu_baseline"] = base
     dev.free(dx); dev.free(dy)
     if comm:
         comm.close()
@@ -416,10 +422,50 @@ def run_gemm(sm, dev, ranks, peaks, W, K, sizes):
         tf = 2.0 * size * size * size / (t * 1e-3) / 1e12
         out.append({"name": "gemm_fp32_3xtf32_%d" % size, "metric": "tflops", "value": tf, "unit": "TFLOP/s",
                     "ms_per_step": t, "sharding": "A/C row blocks of %d rows per GPU, B replicated" % M,
-                    "roofline": roofline("tensor", tf / G, peak, "TFLOP/s", None, peaks),
+                    "roofline": dict(roofline("tensor", tf / G, peak, "TFLOP/s", None, peaks),
+                                     frac_of_sustained_peak=tf / G / (peaks["bf16_tflops_sustained"] / 6.0)),
                     "hbm_bytes": 4.0 * (M * size + size * size + M * size)})
         for p in (a, b, c):
             dev.free(p)
+    return out
+
+
+def cpu_baselines_other(seconds_each=3.0):
+    """The CPU checker timed on bounded samples of the other four workloads, all
+    host threads over disjoint ranges (the reference compiler's x86-64 objects when
+    they are built here). Returned keyed by workload family."""
+    import oracle
+    import booth_b200 as sm
+    orc = oracle.load()
+    out = {}
+
+    def run(fn, units, unit, sample):
+        fn()
+        reps, t0 = 0, time.perf_counter()
+        while True:
+            fn()
+            reps += 1
+            dt = time.perf_counter() - t0
+            if dt >= seconds_each or reps >= 50:
+                break
+        return {"value": units * reps / dt, "unit": unit, "cores": orc.cores, "kind": orc.kind,
+                "sample": "%s x %d repetitions, %d threads" % (sample, reps, orc.cores)}
+
+    m = 1 << 26
+    x = sm.fill_host(m, SEED, 0, sm.FILL_F32_PM1, threads=orc.cores)
+    y = sm.fill_host(m, SEED, 1, sm.FILL_F32_PM1, threads=orc.cores)
+    out["vadd"] = run(lambda: orc.vadd(x, y), 12.0 * m / 1e9, "GB/s", "vector add on 2^26 elements")
+    vi = sm.fill_host(m, SEED + 2, 0, sm.FILL_I32_1000, threads=orc.cores)
+    out["reduce_i32"] = run(lambda: orc.reduce_i32(vi), 4.0 * m / 1e9, "GB/s", "int32 sum of 2^26 elements")
+    vf = sm.fill_host(m, SEED + 2, 1, sm.FILL_F32_01, threads=orc.cores)
+    out["reduce_f32"] = run(lambda: orc.reduce_f32(vf), 4.0 * m / 1e9, "GB/s", "fp32 sum of 2^26 elements")
+    g = 1024
+    a = sm.fill_host(g * g, SEED + 3, 0, sm.FILL_F32_PM1).reshape(g, g)
+    b = sm.fill_host(g * g, SEED + 3, 1, sm.FILL_F32_PM1).reshape(g, g)
+    out["gemm"] = run(lambda: orc.matmul(a, b), 2.0 * g ** 3 / 1e12, "TFLOP/s", "1024^3 GEMM by 4x4x2 tiles")
+    prm = sm.asian_params(k0=SEED + 5)
+    npth = 1 << 20
+    out["asian"] = run(lambda: orc.asian(prm, 0, npth), float(npth), "paths/s", "2^20 paths x 252 steps")
     return out
 
 
