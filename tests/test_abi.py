@@ -28,7 +28,7 @@ def test_headers_declare_the_reference_api():
 
 def test_library_exports_every_declared_symbol(sm):
     handle = C.CDLL(sm.LIB_PATH)
-    declared = _declared("bc_runtime.h") + _declared("booth_sm100.h")
+    declared = _declared("bc_runtime.h") + _declared("booth_sm100.h") + _declared("lf_gpu.h")
     assert len(declared) > 40
     for name in declared:
         assert hasattr(handle, name), "libbooth_sm100.so does not export %s" % name
@@ -102,6 +102,22 @@ def test_cpu_launcher_symbol_aborts_without_a_gpu(sm):
     assert res.returncode != 0
     assert "sum" not in res.stdout
     assert "there is no CPU fallback" in res.stderr
+
+
+def test_offload_abi_declares_the_reference_functions_and_dies_loudly(sm):
+    # src/runtime/lf_gpu.h:21-35: eight void-returning functions with no error
+    # channel, so a device that cannot be opened ends the process with status 1
+    # and one line on stderr (src/runtime/lf_gpu.c:55-59), never a CPU run.
+    assert _declared("lf_gpu.h") == sorted(
+        ["lfortran_gpu_init", "lfortran_gpu_shutdown", "lfortran_gpu_load_kernel", "lfortran_gpu_release_kernel",
+         "lfortran_gpu_set_buffer_arg", "lfortran_gpu_set_scalar_arg", "lfortran_gpu_launch", "lfortran_gpu_sync"])
+    code = ("import ctypes as C, booth_b200 as b\n"
+            "L=b.lib(); L.lfortran_gpu_init.restype=C.c_void_p; L.lfortran_gpu_shutdown(None); print('before')\n"
+            "L.lfortran_gpu_init(); print('after')\n")
+    res = _run(code, {"BOOTH_CUDA_LIB": "/nonexistent/libcuda.so.1"})
+    assert res.returncode == 1
+    assert "before" in res.stdout and "after" not in res.stdout
+    assert "lf_gpu_sm100: sm100_rt_init failed (rc=-1)" in res.stderr
 
 
 def test_python_layer_raises_when_library_is_missing(sm, tmp_path):
