@@ -82,6 +82,7 @@ _SIGNATURES = {
     "sm100_rt_launch_packed": (C.c_int, [_dev, C.POINTER(Kern)] + [C.c_uint32] * 7 + [C.c_void_p, C.c_uint32]),
     "sm100_rt_sync": (C.c_int, [_dev]),
     "sm100_rt_hostalloc": (C.c_int, [_dev, C.POINTER(C.c_void_p), C.c_size_t]),
+    "sm100_rt_hostmap": (C.c_int, [_dev, C.POINTER(C.c_void_p), C.POINTER(C.c_uint64), C.c_size_t]),
     "sm100_rt_hostfree": (None, [_dev, C.c_void_p]),
     "sm100_rt_tic": (C.c_int, [_dev]),
     "sm100_rt_toc": (C.c_int, [_dev, C.POINTER(C.c_float)]),

@@ -26,7 +26,7 @@ SO = os.path.join(LIB, "libbooth_sm100.so")
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo",
               "-std=c++17", "--fmad=true", "-Xptxas", "-v"]
-C_SOURCES = ["sm100_shim.c", "bc_runtime.c", "sm100_ops.c", "sm100_comm.c", "rt_sm100.c", "lf_gpu_sm100.c"]
+C_SOURCES = ["sm100_shim.c", "bc_runtime.c", "sm100_ops.c", "sm100_comm.c", "rt_sm100.c", "lf_gpu_sm100.c", "nv_rt_sm100.c"]
 
 
 def _cuda_home():
@@ -75,7 +75,7 @@ def build(force=False, verbose=False):
               "-std=c++17", "-Xcompiler", "-fPIC", "-I", INCLUDE, "-c", noalloc_cu, "-o", noalloc_o], log)
     deps = csrc + [noalloc_o, CUBIN, os.path.join(CSRC, "image.S"), os.path.join(CSRC, "sm100_internal.h"),
                    os.path.join(INCLUDE, "booth_sm100.h"), os.path.join(INCLUDE, "bc_runtime.h"),
-                   os.path.join(INCLUDE, "rt_sm100.h"), os.path.join(INCLUDE, "lf_gpu.h")]
+                   os.path.join(INCLUDE, "rt_sm100.h"), os.path.join(INCLUDE, "lf_gpu.h"), os.path.join(INCLUDE, "nv_rt.h")]
     if force or not _newer(SO, deps):
         _run(["gcc", "-std=c99", "-O2", "-fPIC", "-shared", "-Wall", "-Wextra",
               "-Wno-unused-parameter", "-fvisibility=default",

@@ -19,6 +19,7 @@ typedef struct sm100_api {
     CUresult (*CtxSetCurrent)(CUcontext);
     CUresult (*CtxGetCurrent)(CUcontext *);
     CUresult (*ModuleLoadData)(CUmodule *, const void *);
+    CUresult (*ModuleLoadDataEx)(CUmodule *, const void *, unsigned, CUjit_option *, void **);
     CUresult (*ModuleUnload)(CUmodule);
     CUresult (*ModuleGetFunction)(CUfunction *, CUmodule, const char *);
     CUresult (*FuncGetAttribute)(int *, CUfunction_attribute, CUfunction);
@@ -36,6 +37,7 @@ typedef struct sm100_api {
     CUresult (*MemsetD8Async)(CUdeviceptr, unsigned char, size_t, CUstream);
     CUresult (*MemHostAlloc)(void **, size_t, unsigned);
     CUresult (*MemFreeHost)(void *);
+    CUresult (*MemHostGetDevicePointer)(CUdeviceptr *, void *, unsigned);
     CUresult (*StreamCreate)(CUstream *, unsigned);
     CUresult (*StreamDestroy)(CUstream);
     CUresult (*StreamSynchronize)(CUstream);

@@ -58,6 +58,7 @@ static int api_load(void)
     SYM(CtxSetCurrent, "cuCtxSetCurrent");
     SYM(CtxGetCurrent, "cuCtxGetCurrent");
     SYM(ModuleLoadData, "cuModuleLoadData");
+    SYM(ModuleLoadDataEx, "cuModuleLoadDataEx");
     SYM(ModuleUnload, "cuModuleUnload");
     SYM(ModuleGetFunction, "cuModuleGetFunction");
     SYM(FuncGetAttribute, "cuFuncGetAttribute");
@@ -75,6 +76,7 @@ static int api_load(void)
     SYM(MemsetD8Async, "cuMemsetD8Async");
     SYM(MemHostAlloc, "cuMemHostAlloc");
     SYM(MemFreeHost, "cuMemFreeHost");
+    SYM(MemHostGetDevicePointer, "cuMemHostGetDevicePointer_v2");
     SYM(StreamCreate, "cuStreamCreate");
     SYM(StreamDestroy, "cuStreamDestroy_v2");
     SYM(StreamSynchronize, "cuStreamSynchronize");
@@ -365,10 +367,23 @@ int sm100_rt_load(sm100_dev_t *dev, const char *path, const char *name, sm100_ke
     fclose(fp);
     if (got != (size_t)sz) { free(buf); fprintf(stderr, "sm100_rt: short read on '%s'\n", path); return SM100_ERR_IO; }
     buf[sz] = 0;
+    /* The file may be a cubin, a fatbin or PTX text (the reference's launcher loads
+     * PTX, src/nvidia/nv_rt.c:172-248); for PTX the driver compiles it here, so ask
+     * for its error log and print it when the load fails. */
     CUmodule mod;
-    CUresult cr = dev->api->ModuleLoadData(&mod, buf);
+    char jit_log[4096];
+    jit_log[0] = 0;
+    CUjit_option opts[2] = { CU_JIT_ERROR_LOG_BUFFER, CU_JIT_ERROR_LOG_BUFFER_SIZE_BYTES };
+    void *vals[2] = { jit_log, (void *)(size_t)sizeof jit_log };
+    CUresult cr = dev->api->ModuleLoadDataEx(&mod, buf, 2, opts, vals);
     free(buf);
-    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "cuModuleLoadData", cr);
+    if (cr != CUDA_SUCCESS) {
+        char what[600];
+        snprintf(what, sizeof what, "loading '%s'", path);
+        jit_log[sizeof jit_log - 1] = 0;
+        if (jit_log[0]) fprintf(stderr, "sm100_rt: compiler log for '%s':\n%s\n", path, jit_log);
+        return sm100_fail(dev, what, cr);
+    }
     return kern_from_module(dev, mod, 1, name, out);
 }
 
@@ -471,6 +486,26 @@ int sm100_rt_hostalloc(sm100_dev_t *dev, void **hp, size_t size)
     if (rc != SM100_OK) return rc;
     CUresult cr = dev->api->MemHostAlloc(hp, size ? size : 1, CU_MEMHOSTALLOC_PORTABLE);
     return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "pinned host alloc", cr);
+}
+
+int sm100_rt_hostmap(sm100_dev_t *dev, void **hp, sm100_ptr_t *dp, size_t size)
+{
+    if (!hp || !dp) return fail_arg(dev, "sm100_rt_hostmap: NULL out");
+    *hp = NULL;
+    *dp = 0;
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    CUresult cr = dev->api->MemHostAlloc(hp, size ? size : 1, CU_MEMHOSTALLOC_PORTABLE | CU_MEMHOSTALLOC_DEVICEMAP);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "mapped host alloc", cr);
+    CUdeviceptr d = 0;
+    cr = dev->api->MemHostGetDevicePointer(&d, *hp, 0);
+    if (cr != CUDA_SUCCESS) {
+        dev->api->MemFreeHost(*hp);
+        *hp = NULL;
+        return sm100_fail(dev, "device address of mapped host memory", cr);
+    }
+    *dp = (sm100_ptr_t)d;
+    return SM100_OK;
 }
 
 void sm100_rt_hostfree(sm100_dev_t *dev, void *hp)

@@ -77,7 +77,8 @@ int  sm100_rt_ordinal(const sm100_dev_t *dev);
 const char *sm100_rt_errs(const sm100_dev_t *dev);
 
 /* Replaces nv_rt_load (src/nvidia/nv_rt.c:172-248): path names a cubin or
- * fatbin built for sm_100a. */
+ * fatbin built for sm_100a, or PTX text, which the driver compiles at load (its
+ * error log is printed when that fails). */
 int  sm100_rt_load(sm100_dev_t *dev, const char *path, const char *name,
                    sm100_kern_t *out);
 /* Same, from the kernel image embedded in the library. */
@@ -116,6 +117,10 @@ int  sm100_rt_sync(sm100_dev_t *dev);
 
 /* Pinned host memory; replace nv_rt_mmap / nv_rt_mfre (src/nvidia/nv_rt.c:348-381). */
 int  sm100_rt_hostalloc(sm100_dev_t *dev, void **hp, size_t size);
+/* Pinned host memory that kernels can address: *hp is the host pointer, *dp the
+ * device address of the same bytes (nv_rt_mmap, src/nvidia/nv_rt.c:348-375).
+ * Released with sm100_rt_hostfree. */
+int  sm100_rt_hostmap(sm100_dev_t *dev, void **hp, sm100_ptr_t *dp, size_t size);
 void sm100_rt_hostfree(sm100_dev_t *dev, void *hp);
 
 /* Device-side timing on the device's stream: tic records an event, toc records
