@@ -5,8 +5,12 @@
 // launcher looks kernels up by bare name and the CALLER picks the launch
 // geometry (examples/launch_saxpy.c:83-87 launches one thread per element).
 // They are therefore correct for any grid and block shape: the threads of the
-// launch are flattened and walk the vectors in tiles of 128-bit accesses, a
-// launch with more threads than 16-byte chunks simply leaves the surplus idle.
+// launch are flattened and walk the vectors in tiles of 256-bit accesses. A
+// launch with many more blocks than the device can hold (one thread per element
+// is eight times more threads than 32-byte chunks) keeps only its first blocks
+// working; the others retire at once. vadd_stream and saxpy_stream are the same
+// bodies without that test, for the library's own launches, whose geometry the
+// host side picks.
 //
 // Arithmetic matches the reference's x86-64 backend bit for bit: the product
 // and the sum of saxpy are rounded separately (mulss then addss,
@@ -16,11 +20,16 @@
 // Memory behaviour: every element is touched once. When the pointers allow it a
 // thread moves 32 bytes per instruction (256-bit ld/st.global) and keeps two such
 // loads per input in flight; a warp's accesses are contiguous 1 KiB rows. The
-// host launches 3 blocks of 128 threads per SM: on a B200 about 50-100 KB of
-// loads in flight per SM saturate HBM, and more resident threads measurably
-// lower the rate (6.9 TB/s at 384 threads per SM against 6.4 TB/s at 2048).
+// host launches 5 blocks of 128 threads per SM (12 for vectors under 2^26
+// elements, where the ramp of a 30 us launch dominates): on a B200 about 80 KB
+// of loads in flight per SM saturate HBM, and more resident threads measurably
+// lower the rate (6.9 TB/s at 640 threads per SM against 6.4 TB/s at 2048).
 // Algorithmic traffic is 12 bytes per element for both kernels.
 #include "common.cuh"
+
+// Threads per SM that an oversized launch of the by-name kernels keeps working.
+#define STREAM_KEEP_LONG 640      // vectors of 2^26 elements and more
+#define STREAM_KEEP_SHORT 1536
 
 #define UNROLL 4      // 128-bit path: independent 16-byte loads per input per thread
 #define UNROLL8 2     // 256-bit path: independent 32-byte loads per input per thread
@@ -54,20 +63,37 @@ __device__ __forceinline__ float4 axpy4(float a, float4 x, float4 y)
                        __fadd_rn(__fmul_rn(a, x.z), y.z), __fadd_rn(__fmul_rn(a, x.w), y.w));
 }
 
-// One body for both kernels: out[i] = op(x[i], y[i]) with op = x + y (SAXPY false)
-// or fl(fl(a*x) + y) (SAXPY true). Three paths by pointer alignment: 32-byte
+// One body for all four kernels: out[i] = op(x[i], y[i]) with op = x + y (SAXPY
+// false) or fl(fl(a*x) + y) (SAXPY true). Three paths by pointer alignment: 32-byte
 // vectors, 16-byte vectors, scalars; each ends with a scalar tail.
+//
+// ANY_LAUNCH: the geometry is the caller's. Blocks are handed to the SMs in index
+// order, so when the launch has more blocks than `keep` (as many as the host side
+// would launch itself) the first `keep` start together and stream the whole vector
+// while the surplus blocks come and go beside them without touching memory; how
+// fast the SMs retire empty blocks (about 1.5 per ns) then sets the pace.
 template <bool SAXPY>
 __device__ __forceinline__ float op1(float a, float x, float y)
 {
     return SAXPY ? __fadd_rn(__fmul_rn(a, x), y) : __fadd_rn(x, y);
 }
 
-template <bool SAXPY>
+template <bool SAXPY, bool ANY_LAUNCH>
 __device__ __forceinline__ void stream_body(const float *x, const float *y, float *out, float a, long long n)
 {
     const unsigned tid = flat_tid(), B = flat_bdim();
-    const unsigned long long bid = flat_bid(), G = flat_gdim();
+    const unsigned long long bid = flat_bid();
+    unsigned long long G = flat_gdim();
+    if (ANY_LAUNCH) {
+        unsigned nsm;
+        asm("mov.u32 %0, %%nsmid;" : "=r"(nsm));
+        const unsigned per_sm = (n < (1ll << 26) ? STREAM_KEEP_SHORT : STREAM_KEEP_LONG) / B;
+        const unsigned long long keep = (unsigned long long)nsm * (per_sm ? per_sm : 1u);
+        if (G > keep) {
+            if (bid >= keep) return;
+            G = keep;
+        }
+    }
     const uintptr_t bits = (uintptr_t)x | (uintptr_t)y | (uintptr_t)out;
     long long done;                     // elements covered by the vector part
     if ((bits & 31) == 0) {
@@ -142,13 +168,22 @@ extern "C" __global__ void vector_add(const float *x, const float *y, float *out
                                       int n_elements, int block_size)
 {
     (void)block_size;
-    stream_body<false>(x, y, out, 0.0f, (long long)n_elements);
+    stream_body<false, true>(x, y, out, 0.0f, (long long)n_elements);
+}
+extern "C" __global__ void vadd_stream(const float *x, const float *y, float *out, int n_elements, int block_size)
+{
+    (void)block_size;
+    stream_body<false, false>(x, y, out, 0.0f, (long long)n_elements);
 }
 
 // y[i] = a*x[i] + y[i] for i < n, product and sum rounded separately.
 extern "C" __global__ void saxpy(float *y, const float *x, float a, int n)
 {
-    stream_body<true>(x, y, y, a, (long long)n);
+    stream_body<true, true>(x, y, y, a, (long long)n);
+}
+extern "C" __global__ void saxpy_stream(float *y, const float *x, float a, int n)
+{
+    stream_body<true, false>(x, y, y, a, (long long)n);
 }
 
 // ---- seeded inputs -------------------------------------------------------

@@ -52,7 +52,9 @@ def test_launch_saxpy_flow(sm, bc):
 
 
 @pytest.mark.parametrize("grid,block", [((1, 1, 1), (1, 1, 1)), ((0, 0, 0), (0, 0, 0)), ((7, 3, 2), (33, 3, 1)),
-                                        ((40, 1, 1), (256, 1, 1)), ((2, 2, 1), (8, 8, 4))])
+                                        ((40, 1, 1), (256, 1, 1)), ((2, 2, 1), (8, 8, 4)),
+                                        # more blocks than the tuned geometry: only the first ones work
+                                        ((5000, 1, 1), (256, 1, 1)), ((70, 30, 1), (1024, 1, 1)), ((3000, 1, 1), (33, 3, 1))])
 def test_any_launch_geometry_and_oversized_args(sm, bc, oracle_lib, grid, block):
     L, d = bc
     n = 10001

@@ -121,6 +121,20 @@ def test_reference_offload_layer_over_nv_rt(sm):
     assert "saxpy x2   n=70001: 0 mismatches" in res.stdout and "lf_offload: ok" in res.stdout
 
 
+@pytest.mark.gpu
+def test_timing_program_under_both_launch_shapes(sm):
+    # examples/nv_rt_time.c: the by-name saxpy under a one-thread-per-element launch
+    # (most blocks retire at once) and under a fixed grid; the data must come back intact.
+    exe = os.path.join(EXAMPLES, "nv_rt_time")
+    if not os.path.exists(exe):
+        pytest.skip("build/examples/nv_rt_time was not built")
+    for name in ("saxpy", "saxpy_stream"):
+        res = subprocess.run([exe, sm.CUBIN_PATH, "22", "5", name], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                             text=True, timeout=120)
+        assert res.returncode == 0, res.stdout + res.stderr
+        assert "one thread per element" in res.stdout and "nv_rt_time: ok" in res.stdout
+
+
 @pytest.fixture()
 def nv(sm):
     L = _bind(sm.lib())
