@@ -233,3 +233,68 @@ def test_canonical_kernels_by_name(sm, bc):
         assert abs(float(zero[0]) - float(v.astype(np.float64).sum())) <= 2e-5 * n * 0.5
     for p in (da, db, dc, dv, do):
         L.bc_free(C.byref(d), p)
+
+
+def test_dot_product_and_tinygrad_reduction_by_name(sm, bc):
+    """dot_product (tests/canonical.cu:149-161) and the tinygrad attention reduction
+    r_2_1024_16_64 (tests/tg_reduce.cu:4-26) loaded by name through bc_*."""
+    L, d = bc
+    k = sm.BcKernel()
+
+    class DotArgs(C.Structure):
+        _fields_ = [("out", C.c_void_p), ("a", C.c_void_p), ("b", C.c_void_p), ("n", C.c_int)]
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"dot_product", C.byref(k)) == 0
+    n = 250007
+    a, b = sm.fill_host(n, 63, 0, 0), sm.fill_host(n, 63, 1, 0)
+    da, db, do = L.bc_alloc(C.byref(d), n * 4), L.bc_alloc(C.byref(d), n * 4), L.bc_alloc(C.byref(d), 4)
+    L.bc_copy_h2d(C.byref(d), da, a.ctypes.data, n * 4); L.bc_copy_h2d(C.byref(d), db, b.ctypes.data, n * 4)
+    exact = float((a.astype(np.float64) * b.astype(np.float64)).sum())
+    for grid, block in (((128, 1, 1), (256, 1, 1)), ((5, 3, 1), (40, 2, 1))):
+        start = np.array([1.5], np.float32)                  # *result is added to, not overwritten
+        L.bc_copy_h2d(C.byref(d), do, start.ctypes.data, 4)
+        args = DotArgs(do, da, db, n)
+        assert L.bc_dispatch(C.byref(d), C.byref(k), *grid, *block, C.byref(args), C.sizeof(args)) == 0
+        L.bc_copy_d2h(C.byref(d), start.ctypes.data, do, 4)
+        assert abs(float(start[0]) - 1.5 - exact) <= 1e-4 * np.sqrt(n)
+    L.bc_unload_kernel(C.byref(d), C.byref(k))
+    for p in (da, db, do):
+        L.bc_free(C.byref(d), p)
+
+    class TgArgs(C.Structure):
+        _fields_ = [("data0", C.c_void_p), ("data1", C.c_void_p), ("data2", C.c_void_p), ("data3", C.c_void_p),
+                    ("start_pos", C.c_int)]
+    assert L.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"r_2_1024_16_64", C.byref(k)) == 0
+    rng = np.random.default_rng(64)
+    start_pos = 3
+    data1 = rng.integers(0, 4, 16 * 64).astype(np.int32)            # 1024 flags drawn from four keys
+    data2 = rng.integers(0, 4, start_pos + 2).astype(np.int32)
+    data3 = sm.fill_host(16 * 64 * 1024, 64, 0, 0)
+    data3[12345] = np.inf                                            # a masked-out infinity must still poison its sum
+    cube = data3.reshape(16, 64, 1024)                               # [l][r][x]
+    want = np.zeros((2, 1024), np.float32)
+    with np.errstate(invalid="ignore"):
+        for y in range(2):
+            flag = (data1.reshape(16, 64) == data2[start_pos + y]).astype(np.float32)
+            part = np.zeros((16, 1024), np.float32)
+            for r in range(64):                                      # r ascending inside a thread
+                part = part + flag[:, r:r + 1] * cube[:, r, :]
+            tot = np.zeros(1024, np.float32)
+            for l in range(16):                                      # then the sixteen partials in order
+                tot = tot + part[l]
+            want[y] = tot
+    bufs = [L.bc_alloc(C.byref(d), x.nbytes) for x in (want, data1, data2, data3)]
+    for p, x in zip(bufs[1:], (data1, data2, data3)):
+        L.bc_copy_h2d(C.byref(d), p, x.ctypes.data, x.nbytes)
+    args = TgArgs(bufs[0], bufs[1], bufs[2], bufs[3], start_pos)
+    assert L.bc_dispatch(C.byref(d), C.byref(k), 1024, 2, 1, 16, 1, 1, C.byref(args), C.sizeof(args)) == 0
+    got = np.empty((2, 1024), np.float32)
+    L.bc_copy_d2h(C.byref(d), got.ctypes.data, bufs[0], got.nbytes)
+    nan = np.isnan(want)                                             # NaN payloads differ between x86 and the GPU
+    assert nan.sum() + np.isinf(want).sum() >= 1
+    assert np.array_equal(np.isnan(got), nan)
+    assert np.array_equal(got[~nan].view(np.uint32), want[~nan].view(np.uint32))
+    # more than the 16 threads the kernel is built for is refused by the launch, not run wrongly
+    assert L.bc_dispatch(C.byref(d), C.byref(k), 1024, 2, 1, 32, 1, 1, C.byref(args), C.sizeof(args)) != 0
+    L.bc_unload_kernel(C.byref(d), C.byref(k))
+    for p in bufs:
+        L.bc_free(C.byref(d), p)
