@@ -6,11 +6,12 @@
 // geometry (examples/launch_saxpy.c:83-87 launches one thread per element).
 // They are therefore correct for any grid and block shape: the threads of the
 // launch are flattened and walk the vectors in tiles of 256-bit accesses. A
-// launch with many more blocks than the device can hold (one thread per element
-// is eight times more threads than 32-byte chunks) keeps only its first blocks
-// working; the others retire at once. vadd_stream and saxpy_stream are the same
-// bodies without that test, for the library's own launches, whose geometry the
-// host side picks.
+// launch far larger than any tuned one (one thread per element is eight times
+// more threads than 32-byte chunks) keeps only its first blocks working; the
+// others retire at once. The library launches saxpy under this name too;
+// vadd_stream is the vector add body without that test for the library's own
+// launches (with the test it needs more than the 48 registers the by-name kernels
+// are held to, see below, and spills).
 //
 // Arithmetic matches the reference's x86-64 backend bit for bit: the product
 // and the sum of saxpy are rounded separately (mulss then addss,
@@ -19,11 +20,12 @@
 //
 // Memory behaviour: every element is touched once. When the pointers allow it a
 // thread moves 32 bytes per instruction (256-bit ld/st.global) and keeps two such
-// loads per input in flight; a warp's accesses are contiguous 1 KiB rows. The
-// host launches 5 blocks of 128 threads per SM (12 for vectors under 2^26
-// elements, where the ramp of a 30 us launch dominates): on a B200 about 80 KB
-// of loads in flight per SM saturate HBM, and more resident threads measurably
-// lower the rate (6.9 TB/s at 640 threads per SM against 6.4 TB/s at 2048).
+// loads per input in flight; a warp's accesses are contiguous 1 KiB rows. For
+// vectors of 2^28 elements and more the host launches three persistent blocks of
+// 128 threads per SM: HBM throughput on a B200 peaks sharply at 384 threads per
+// SM (6.9 TB/s for both kernels, 6.5 at 640). Shorter vectors get up to 128
+// blocks per SM, one tile each, so that the hardware scheduler evens out the two
+// ends of a launch that lasts tens of microseconds.
 // Algorithmic traffic is 12 bytes per element for both kernels.
 #include "common.cuh"
 
@@ -68,8 +70,8 @@ __device__ __forceinline__ float4 axpy4(float a, float4 x, float4 y)
 // vectors, 16-byte vectors, scalars; each ends with a scalar tail.
 //
 // ANY_LAUNCH: the geometry is the caller's. Blocks are handed to the SMs in index
-// order, so when the launch has more blocks than `keep` (as many as the host side
-// would launch itself) the first `keep` start together and stream the whole vector
+// order, so when the launch has more than 128 blocks per SM the first `keep` (a
+// few per SM) start together and stream the whole vector
 // while the surplus blocks come and go beside them without touching memory; how
 // fast the SMs retire empty blocks (about 1.5 per ns) then sets the pace.
 template <bool SAXPY>
@@ -87,9 +89,9 @@ __device__ __forceinline__ void stream_body(const float *x, const float *y, floa
     if (ANY_LAUNCH) {
         unsigned nsm;
         asm("mov.u32 %0, %%nsmid;" : "=r"(nsm));
-        const unsigned per_sm = (n < (1ll << 26) ? STREAM_KEEP_SHORT : STREAM_KEEP_LONG) / B;
-        const unsigned long long keep = (unsigned long long)nsm * (per_sm ? per_sm : 1u);
-        if (G > keep) {
+        if (G > 128ull * nsm) {                     // far beyond any tuned launch
+            const unsigned per_sm = (n < (1ll << 26) ? STREAM_KEEP_SHORT : STREAM_KEEP_LONG) / B;
+            const unsigned long long keep = (unsigned long long)nsm * (per_sm ? per_sm : 1u);
             if (bid >= keep) return;
             G = keep;
         }
@@ -164,8 +166,12 @@ __device__ __forceinline__ void stream_body(const float *x, const float *y, floa
 
 // out[i] = x[i] + y[i] for i < n_elements. block_size is the Triton BLOCK_SIZE
 // parameter of the reference kernel; the geometry comes from the launch itself.
-extern "C" __global__ void vector_add(const float *x, const float *y, float *out,
-                                      int n_elements, int block_size)
+// The by-name kernels are held to 48 registers: under a one-thread-per-element
+// launch of 256-thread blocks that leaves room for five blocks per SM, two that
+// work and three slots through which the empty ones pass (4.3 TB/s against 3.5
+// with four).
+extern "C" __global__ void __maxnreg__(48) vector_add(const float *x, const float *y, float *out,
+                                                      int n_elements, int block_size)
 {
     (void)block_size;
     stream_body<false, true>(x, y, out, 0.0f, (long long)n_elements);
@@ -177,13 +183,9 @@ extern "C" __global__ void vadd_stream(const float *x, const float *y, float *ou
 }
 
 // y[i] = a*x[i] + y[i] for i < n, product and sum rounded separately.
-extern "C" __global__ void saxpy(float *y, const float *x, float a, int n)
+extern "C" __global__ void __maxnreg__(48) saxpy(float *y, const float *x, float a, int n)
 {
     stream_body<true, true>(x, y, y, a, (long long)n);
-}
-extern "C" __global__ void saxpy_stream(float *y, const float *x, float a, int n)
-{
-    stream_body<true, false>(x, y, y, a, (long long)n);
 }
 
 // ---- seeded inputs -------------------------------------------------------

@@ -40,20 +40,19 @@ static int bad_arg(sm100_dev_t *dev, const char *what)
 #define SCRATCH_TICKET   SM100_SCRATCH_TICKET
 #define SCRATCH_PARTIALS SM100_SCRATCH_PARTIALS
 
-/* Streaming kernels: 128-thread blocks, `dflt` of them per SM; one block
- * iteration covers 128 threads x 2 x 32 bytes per input. HBM throughput on a
- * B200 peaks sharply at about 80 KB of loads in flight per SM (measured for
- * saxpy at 2^30 elements: 5.8 TB/s at 3 blocks per SM, 6.5 at 4, 6.9 at 5, 6.7 at
- * 6, 6.5 at 8 and above), so the grid is that small multiple of the SM count,
- * capped by the work there is. BOOTH_SM100_STREAM_BPSM / _BLOCK override it. */
-static unsigned stream_grid(sm100_dev_t *dev, long long n, unsigned block, unsigned unroll, int dflt)
+/* Streaming kernels: 128-thread blocks; one block iteration (a tile) covers 128
+ * threads x 2 x 32 bytes per input. Vectors of 2^28 elements and more get three
+ * persistent blocks per SM: HBM throughput on a B200 peaks sharply at 384 threads
+ * per SM for both kernels (saxpy at 2^30 elements: 6.94 TB/s at 3 blocks per SM,
+ * 6.52 at 5, 6.73 at 32; vector add at 2^29: 6.94 at 3, 6.53 at 5, 6.79 at 32).
+ * Shorter vectors stream for tens of microseconds and are dominated by the two
+ * ends of the launch: up to 128 blocks per SM, in practice one tile each, let the
+ * hardware scheduler even those out (saxpy at 2^24: 7.5 TB/s against 6.1 at 3
+ * persistent blocks per SM; vector add: 6.45 against 5.96; at 2^27 the two
+ * geometries meet). BOOTH_SM100_STREAM_BPSM / _BLOCK override. */
+static unsigned stream_grid(sm100_dev_t *dev, long long n, unsigned block, unsigned unroll)
 {
-    /* Vectors that stream for only a few tens of microseconds (2^24 elements: 32 us)
-     * are dominated by the ramp at both ends of the launch; more, shorter blocks
-     * fill the machine sooner (measured at 2^24: 6.38 TB/s at 12 blocks per SM
-     * against 6.29 at 5). */
-    if (n < (1ll << 26)) dflt = 12;
-    const int bpsm = env_int("BOOTH_SM100_STREAM_BPSM", dflt, 1, 64);
+    const int bpsm = env_int("BOOTH_SM100_STREAM_BPSM", n < (1ll << 28) ? 128 : 3, 1, 128);
     long long tiles = ((n >> 3) + (long long)block * unroll - 1) / ((long long)block * unroll);
     long long g = (long long)dev->sm_count * bpsm;
     if (tiles < g) g = tiles;
@@ -84,7 +83,7 @@ int booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y, sm100_ptr_t
     int ni = (int)n, bs = 256;
     const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &x, &y, &out, &ni, &bs };
-    return sm100_launch_k(dev, SM100_K_VADD, stream_grid(dev, n, block, 2, 5), block, 0, args);
+    return sm100_launch_k(dev, SM100_K_VADD, stream_grid(dev, n, block, 2), block, 0, args);
 }
 
 int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, long long n)
@@ -96,7 +95,7 @@ int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, l
     int ni = (int)n;
     const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &y, &x, &a, &ni };
-    return sm100_launch_k(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 2, 5), block, 0, args);
+    return sm100_launch_k(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 2), block, 0, args);
 }
 
 /* Reductions: 256-thread blocks, eight 16-byte loads per thread in flight. The

@@ -128,7 +128,7 @@ def test_timing_program_under_both_launch_shapes(sm):
     exe = os.path.join(EXAMPLES, "nv_rt_time")
     if not os.path.exists(exe):
         pytest.skip("build/examples/nv_rt_time was not built")
-    for name in ("saxpy", "saxpy_stream"):
+    for name in ("saxpy", "vector_add", "vadd_stream"):
         res = subprocess.run([exe, sm.CUBIN_PATH, "22", "5", name], stdout=subprocess.PIPE, stderr=subprocess.PIPE,
                              text=True, timeout=120)
         assert res.returncode == 0, res.stdout + res.stderr
