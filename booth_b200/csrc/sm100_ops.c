@@ -424,8 +424,12 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     CUdeviceptr a_hi = ws, a_lo = ws + a_bytes, b_hi = ws + 2 * a_bytes, b_lo = b_hi + b_bytes;
 
     /* 1. split A, split + transpose B (both write zeros into the padding) */
+    /* one 16-byte chunk per thread: measured 6.0 / 6.7 TB/s at 4096^2 / 8192^2 against
+     * 5.2 / 5.7 for eight persistent blocks per SM */
     void *sa[] = { &a, &a_hi, &a_lo, &M, &K, &Mp, &Kp };
-    if ((rc = sm100_launch_k(dev, SM100_K_GEMM_SPLIT_A, (unsigned)dev->sm_count * 8, 256, 0, sa)) != SM100_OK) return rc;
+    long long a_chunks = (long long)Mp * (Kp / 4), a_grid = (a_chunks + 255) / 256;
+    if (a_grid > 0x7fffffffll) a_grid = 0x7fffffffll;
+    if ((rc = sm100_launch_k(dev, SM100_K_GEMM_SPLIT_A, (unsigned)a_grid, 256, 0, sa)) != SM100_OK) return rc;
     void *sb[] = { &b, &b_hi, &b_lo, &K, &N, &Kp };
     if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(Np / 64), (unsigned)((Kp + 63) / 64), 1, 256, 1, 1, 0, sb)) != SM100_OK)
         return rc;
