@@ -182,6 +182,14 @@ def timed(dev, ranks, warmup, steps, body):
     return ranks.max(ms)
 
 
+def timed_short(dev, ranks, warmup, steps, body, repeats=3):
+    """For kernels that run for tens of microseconds: the median of `repeats` timed
+    runs of K steps each, so that one disturbed half-millisecond window (a clock
+    sample, a host interrupt) does not decide the figure."""
+    runs = sorted(timed(dev, ranks, warmup if r == 0 else 1, steps, body) for r in range(repeats))
+    return runs[len(runs) // 2]
+
+
 def mufu_ceiling(path_steps_per_s, sm_count, clocks):
     """The pricer is bound by the special-function unit, not by HBM or the tensor
     pipe: 3 MUFU operations per path-step on 16 MUFU lanes per SM allow at most
@@ -246,21 +254,21 @@ def run_ours(args):
         sweep = []
         for lg in range(20, args.log2n + 1, 2):
             m = 1 << lg
-            t = timed(dev, ranks, W, K, lambda: dev.saxpy(dy, dx, 2.5, m)) / K
+            t = (timed_short if lg < 28 else timed)(dev, ranks, W, K, lambda: dev.saxpy(dy, dx, 2.5, m)) / K
             sweep.append({"log2n": lg, "ms": t, "gbs_per_gpu": 12.0 * m / (t * 1e-3) / 1e9})
-        workloads.append({"name": "saxpy_sweep", "unit": "GB/s per GPU", "note": "sizes below ~2^25 fit the 126 MB L2",
+        workloads.append({"name": "saxpy_sweep", "unit": "GB/s per GPU", "note": "sizes below ~2^25 fit the 126 MB L2; points below 2^28 are the median of 3 runs of K steps",
                           "points": sweep})
     if "vadd" in want:
         for lg in (LOG2_VADD, min(28, args.log2n)):
             m = 1 << lg
             dz = dev.alloc(m * 4)
-            t = timed(dev, ranks, W, K, lambda: dev.vadd(dx, dy, dz, m)) / K
+            t = (timed_short if lg < 28 else timed)(dev, ranks, W, K, lambda: dev.vadd(dx, dy, dz, m)) / K
             gbs = 12.0 * m / (t * 1e-3) / 1e9
             workloads.append({"name": "vadd_2^%d" % lg, "metric": "hbm_gbs", "value": gbs * G, "unit": "GB/s",
                               "ms_per_step": t,
                               "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s",
                                                    NCU_TRAFFIC_PER_ELEM["vadd"] * m if lg > 26 else None, peaks),
-                              "note": "201 MB working set, partly L2-resident" if lg == LOG2_VADD else "3 GiB working set"})
+                              "note": "201 MB working set, partly L2-resident; median of 3 runs of K steps" if lg == LOG2_VADD else "3 GiB working set"})
             dev.free(dz)
 
     out = dev.alloc(64)
