@@ -127,6 +127,42 @@ def test_full_size_saxpy_windows(sm, dev, oracle_lib):
     dev.free(dx); dev.free(dy)
 
 
+def test_vadd_at_the_configured_size_2_24(sm, dev, oracle_lib):
+    """The benchmark's vector add configuration, whole output compared: N = 2^24,
+    a, b ~ U[-1,1) from the seeded stream, bit-exact against the x86-64 build."""
+    n = 1 << 24
+    x, y = sm.fill_host(n, 0xB0070000, 0, 0), sm.fill_host(n, 0xB0070000, 1, 0)
+    dx, dy, dz = dev.upload(x), dev.upload(y), dev.alloc(n * 4)
+    dev.vadd(dx, dy, dz, n)
+    assert mismatches(dev.download(dz, n, np.float32), oracle_lib.vadd(x, y)) == 0
+    for p in (dx, dy, dz):
+        dev.free(p)
+
+
+def test_full_size_vadd_windows_and_sum(sm, dev, oracle_lib):
+    """N = 2^28 + 5, the persistent-block geometry with a ragged end: windows at the
+    start, an odd middle offset and the end are bit-exact, and over the whole
+    output sum(out) = sum(x) + sum(y) within the fp32-sum tolerance (linearity)."""
+    n = (1 << 28) + 5
+    dx, dy, dz, out = dev.alloc(n * 4), dev.alloc(n * 4), dev.alloc(n * 4), dev.alloc(32)
+    dev.fill(dx, 0, n, 0xB0070000, 0, 1)
+    dev.fill(dy, 0, n, 0xB0070000, 1, 1)
+    dev.vadd(dx, dy, dz, n)
+    w = 1 << 20
+    for first in (0, (n // 2) + 54321, n - w):
+        got = dev.download(dz + 4 * first, w, np.float32)
+        x = sm.fill_host(w, 0xB0070000, 0, 1, first=first)
+        y = sm.fill_host(w, 0xB0070000, 1, 1, first=first)
+        assert mismatches(got, oracle_lib.vadd(x, y)) == 0
+    sums = []
+    for p in (dx, dy, dz):
+        dev.reduce_f32(p, n, out)
+        sums.append(float(dev.download(out, 1, np.float64)[0]))
+    assert abs(sums[2] - (sums[0] + sums[1])) <= 1e-6 * sums[2]
+    for p in (dx, dy, dz, out):
+        dev.free(p)
+
+
 def test_host_vector_calls_pipeline_over_chunks(sm, dev, oracle_lib):
     """booth_sm100_saxpy_host / _vadd_host: host vectors longer than two staging
     chunks (16 Mi elements each), pageable and page-locked, bit-exact."""
