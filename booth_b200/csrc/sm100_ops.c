@@ -99,9 +99,9 @@ int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, l
 }
 
 /* Reductions: 256-thread blocks, eight 16-byte loads per thread in flight. The
- * int32 kernel (32 registers) runs best at 6 blocks per SM (7.1 TB/s at 2^30
- * elements against 6.6 at 4); the fp32 kernel (54 registers, at most 4 blocks
- * fit an SM) at 4 (7.0 TB/s). BOOTH_SM100_REDUCE_BPSM / _BLOCK override. */
+ * int32 kernel (32 registers) runs best at 8 blocks per SM (7.3 TB/s at 2^30
+ * elements against 7.1 at 6 and 6.6 at 4); the fp32 kernel (54 registers, at most
+ * 4 blocks fit an SM) at 4 (7.0 TB/s). BOOTH_SM100_REDUCE_BPSM / _BLOCK override. */
 static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long n, sm100_ptr_t out, int dflt_bpsm)
 {
     int rc = sm100_enter(dev);
@@ -122,7 +122,7 @@ static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long 
 
 int booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
 {
-    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out, 6);
+    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out, 8);
 }
 
 int booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
