@@ -99,6 +99,7 @@ _SIGNATURES = {
     "booth_sm100_reduce_f32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
     "booth_sm100_reduce_f32_noalloc": (C.c_int, [_ptr, C.c_longlong, _ptr, C.c_void_p]),
     "booth_sm100_gemm": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_int, C.c_int, C.c_int]),
+    "booth_sm100_gemm_ex": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_int, C.c_int, C.c_int, C.c_uint]),
     "booth_sm100_asian": (C.c_int, [_dev, C.POINTER(AsianParams), C.c_longlong, C.c_longlong, _ptr]),
     "booth_sm100_asian_paths": (C.c_int, [_dev, C.POINTER(AsianParams), C.c_longlong, C.c_longlong, _ptr, _ptr]),
     # layer 3
@@ -277,8 +278,11 @@ class Device:
     def reduce_f32(self, inp, n, out):
         self._ck("booth_sm100_reduce_f32", lib().booth_sm100_reduce_f32(self._h, inp, n, out))
 
-    def gemm(self, c, a, b, M, N, K):
-        self._ck("booth_sm100_gemm", lib().booth_sm100_gemm(self._h, c, a, b, M, N, K))
+    def gemm(self, c, a, b, M, N, K, b_unchanged=False):
+        if b_unchanged:
+            self._ck("booth_sm100_gemm_ex", lib().booth_sm100_gemm_ex(self._h, c, a, b, M, N, K, 1))
+        else:
+            self._ck("booth_sm100_gemm", lib().booth_sm100_gemm(self._h, c, a, b, M, N, K))
 
     def asian(self, params, path0, npaths, out):
         self._ck("booth_sm100_asian", lib().booth_sm100_asian(self._h, C.byref(params), path0, npaths, out))

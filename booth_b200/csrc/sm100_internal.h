@@ -104,6 +104,8 @@ struct sm100_dev {
     int         stage_ready;
     int         gemm_pending;          /* a GEMM was enqueued since the last status check */
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
+    /* Which B the split planes in the workspace belong to (booth_sm100_gemm_ex reuses them on request). */
+    struct { CUdeviceptr b, planes; int K, N, valid; } gemm_b;
     /* Snapshot of the most recent dispatch (kernel, geometry, first bytes of the
      * parameter block), printed with the labelled buffers when a launch or the
      * wait for it reports an error: the launcher's share of the reference's

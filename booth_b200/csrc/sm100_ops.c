@@ -401,6 +401,12 @@ static int tmap_2d(sm100_dev_t *dev, CUtensorMap *map, CUdeviceptr base, int row
 
 int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t b, int M, int N, int K)
 {
+    return booth_sm100_gemm_ex(dev, c, a, b, M, N, K, 0);
+}
+
+int booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t b, int M, int N, int K,
+                        unsigned flags)
+{
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
     if (!c || !a || !b || M <= 0 || N <= 0 || K <= 0 || ((a | b | c) & 3) ||
@@ -430,9 +436,17 @@ int booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_ptr_t
     long long a_chunks = (long long)Mp * (Kp / 4), a_grid = (a_chunks + 255) / 256;
     if (a_grid > 0x7fffffffll) a_grid = 0x7fffffffll;
     if ((rc = sm100_launch_k(dev, SM100_K_GEMM_SPLIT_A, (unsigned)a_grid, 256, 0, sa)) != SM100_OK) return rc;
-    void *sb[] = { &b, &b_hi, &b_lo, &K, &N, &Kp };
-    if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(Np / 64), (unsigned)((Kp + 63) / 64), 1, 256, 1, 1, 0, sb)) != SM100_OK)
-        return rc;
+    /* The planes of B can stay from the previous call when the caller says B has not
+     * changed and they are still where that call put them. */
+    const int keep_b = (flags & BOOTH_GEMM_B_UNCHANGED) && dev->gemm_b.valid && dev->gemm_b.b == b &&
+                       dev->gemm_b.planes == b_hi && dev->gemm_b.K == K && dev->gemm_b.N == N;
+    if (!keep_b) {
+        void *sb[] = { &b, &b_hi, &b_lo, &K, &N, &Kp };
+        dev->gemm_b.valid = 0;
+        if ((rc = sm100_launch_k3(dev, SM100_K_GEMM_SPLIT_BT, (unsigned)(Np / 64), (unsigned)((Kp + 63) / 64), 1, 256, 1, 1, 0, sb)) != SM100_OK)
+            return rc;
+        dev->gemm_b.b = b; dev->gemm_b.planes = b_hi; dev->gemm_b.K = K; dev->gemm_b.N = N; dev->gemm_b.valid = 1;
+    }
 
     /* 2. the tiled contraction */
     CUtensorMap maps[4];

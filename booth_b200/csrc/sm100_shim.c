@@ -527,6 +527,7 @@ CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes)
     if (bytes <= dev->gemm_ws_bytes) return dev->gemm_ws;
     const sm100_api_t *a = dev->api;
     a->StreamSynchronize(dev->stream);
+    dev->gemm_b.valid = 0;
     if (dev->gemm_ws) { a->MemFree(dev->gemm_ws); dev->gemm_ws = 0; dev->gemm_ws_bytes = 0; }
     CUresult cr = a->MemAlloc(&dev->gemm_ws, bytes);
     if (cr != CUDA_SUCCESS) { sm100_fail(dev, "GEMM workspace alloc", cr); dev->gemm_ws = 0; return 0; }

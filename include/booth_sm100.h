@@ -195,6 +195,16 @@ int  booth_sm100_reduce_f32_noalloc(sm100_ptr_t in, long long n, sm100_ptr_t out
  * multiples of 256 / 256 / 32 waste nothing. */
 int  booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a,
                       sm100_ptr_t b, int M, int N, int K);
+/* The same with flags. BOOTH_GEMM_B_UNCHANGED: the caller states that b, K, N are
+ * those of the previous GEMM on this device and that B's contents have not changed
+ * since; the split, transposed copy of B kept in the workspace is then reused
+ * instead of rebuilt (it is rebuilt anyway when the library finds a different
+ * pointer, shape or workspace). For row blocks of A multiplied against one
+ * replicated B, the reference's sharding of this workload. No counterpart in the
+ * reference. */
+#define BOOTH_GEMM_B_UNCHANGED 1u
+int  booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a,
+                         sm100_ptr_t b, int M, int N, int K, unsigned flags);
 
 /* Asian-option Monte Carlo (src/ocaml/Asian.ml:32-72 with Philox4x32-10 in
  * place of its counter hash). drift = (r - sigma^2/2)*dt and vol = sigma*sqrt(dt)

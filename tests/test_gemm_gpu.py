@@ -156,3 +156,36 @@ d.close()
     assert res.returncode == 0, res.stdout + res.stderr
     assert "reported:" in res.stdout and "gave up waiting on a barrier (code 2" in res.stdout + res.stderr
     assert "after: rel True" in res.stdout
+
+
+def test_gemm_reuses_the_planes_of_an_unchanged_b_only_when_it_may(sm, dev, oracle_lib):
+    """booth_sm100_gemm_ex with BOOTH_GEMM_B_UNCHANGED: same result as the full call
+    when B is unchanged; the flag is ignored when the pointer or the shape differ;
+    and it does what it says when the caller lies (the old B is used), which shows
+    the planes really were reused."""
+    M, N, K = 256, 512, 160
+    a = sm.fill_host(M * K, 71, 0, 0).reshape(M, K)
+    b1 = sm.fill_host(K * N, 71, 1, 0).reshape(K, N)
+    b2 = sm.fill_host(K * N, 71, 2, 0).reshape(K, N)
+    da, db, db2, dc = dev.upload(a), dev.upload(b1), dev.upload(b2), dev.alloc(M * N * 4)
+    want1 = oracle_lib.matmul(a, b1).astype(np.float64)
+    want2 = oracle_lib.matmul(a, b2).astype(np.float64)
+
+    def run(bptr, flag, n=N):
+        dev.zero(dc, M * N * 4)
+        dev.gemm(dc, da, bptr, M, n, K, b_unchanged=flag)
+        dev.sync()
+        return dev.download(dc, (M, N), np.float32).astype(np.float64)
+
+    def close(got, want):
+        return np.linalg.norm(got - want) <= 1e-5 * np.linalg.norm(want)
+
+    assert close(run(db, True), want1)            # nothing to reuse yet: splits B
+    assert close(run(db, True), want1)            # reuses
+    assert close(run(db2, True), want2)           # other pointer: flag ignored
+    assert close(run(db2, True), want2)
+    dev.h2d(db2, b1)                              # B changes behind the library's back ...
+    assert close(run(db2, True), want2)           # ... and the flag keeps the old planes, as documented
+    assert close(run(db2, False), want1)          # the plain call sees the new contents
+    for p in (da, db, db2, dc):
+        dev.free(p)
