@@ -78,3 +78,21 @@ def test_asian_vs_golden(sm, dev, precise):
     dev.asian_paths(prm, 0, n, da, dg)
     ga = dev.download(da, n, np.float32); wa = GOLD["asian_arith_0_1024"].view(np.float32)
     assert np.max(np.abs(ga - wa)) < 2e-3
+
+
+@pytest.mark.parametrize("precise", [1, 0])
+def test_asian_at_the_benchmark_size_vs_golden(sm, dev, precise):
+    """2^26 paths x 252 steps, the benchmark's own run: both price sums against the
+    sums the reference compiler's x86-64 objects produced for the same Philox
+    stream (tests/golden/make_golden.py --full), within the 1e-5 the workload states."""
+    key = "asian_sums_0_%d" % (1 << 26)
+    if key not in GOLD.files:
+        pytest.skip("the full-size sums are not in the fixture file")
+    prm = sm.asian_params(k0=SEED + 5, precise=precise)
+    out = dev.alloc(32)
+    dev.asian(prm, 0, 1 << 26, out)
+    s = dev.download(out, 4, np.float64)
+    want = GOLD[key]
+    rel = [abs(s[i] - want[i]) / want[i] for i in (0, 1)]
+    assert max(rel) <= 1e-5, rel
+    dev.free(out)
