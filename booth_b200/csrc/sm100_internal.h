@@ -50,6 +50,7 @@ typedef struct sm100_api {
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned,
                              unsigned, unsigned, unsigned, unsigned, CUstream,
                              void **, void **);
+    CUresult (*LaunchKernelEx)(const CUlaunchConfig *, CUfunction, void **, void **);   /* optional */
     CUresult (*GetErrorString)(CUresult, const char **);
     CUresult (*TensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
                                      void *, const cuuint64_t *, const cuuint64_t *,
@@ -125,6 +126,11 @@ int  sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
                     unsigned shmem, void **args);
 int  sm100_launch_k3(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsigned gz,
                      unsigned bx, unsigned by, unsigned bz, unsigned shmem, void **args);
+/* The same for kernels that begin with griddepcontrol.wait: the launch may be set
+ * up, and its first blocks placed, while the previous kernel on the stream is still
+ * finishing (programmatic stream serialization). */
+int  sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
+                               unsigned shmem, void **args);
 /* Grows the device-owned scratch / GEMM workspace; returns 0 on failure. */
 CUdeviceptr sm100_scratch(sm100_dev_t *dev, size_t bytes);
 CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes);

@@ -83,7 +83,7 @@ int booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y, sm100_ptr_t
     int ni = (int)n, bs = 256;
     const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &x, &y, &out, &ni, &bs };
-    return sm100_launch_k(dev, SM100_K_VADD, stream_grid(dev, n, block, 2), block, 0, args);
+    return sm100_launch_k_overlapped(dev, SM100_K_VADD, stream_grid(dev, n, block, 2), block, 0, args);
 }
 
 int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, long long n)
@@ -95,7 +95,7 @@ int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, l
     int ni = (int)n;
     const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &y, &x, &a, &ni };
-    return sm100_launch_k(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 2), block, 0, args);
+    return sm100_launch_k_overlapped(dev, SM100_K_SAXPY, stream_grid(dev, n, block, 2), block, 0, args);
 }
 
 /* Reductions: 256-thread blocks, eight 16-byte loads per thread in flight. The

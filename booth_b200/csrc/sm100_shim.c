@@ -87,6 +87,7 @@ static int api_load(void)
     SYM(EventSynchronize, "cuEventSynchronize");
     SYM(EventElapsedTime, "cuEventElapsedTime");
     SYM(LaunchKernel, "cuLaunchKernel");
+    OPT(LaunchKernelEx, "cuLaunchKernelEx");
     SYM(GetErrorString, "cuGetErrorString");
     SYM(TensorMapEncodeTiled, "cuTensorMapEncodeTiled");
 #undef SYM
@@ -641,6 +642,37 @@ int sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
                    unsigned shmem, void **args)
 {
     return sm100_launch_k3(dev, which, grid, 1, 1, block, 1, 1, shmem, args);
+}
+
+int sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
+                              unsigned shmem, void **args)
+{
+    static int enabled = -1;
+    if (enabled < 0) {
+        const char *e = getenv("BOOTH_SM100_PDL");
+        enabled = !(e && e[0] == '0');
+    }
+    if (!enabled || !dev->api->LaunchKernelEx) return sm100_launch_k(dev, which, grid, block, shmem, args);
+    CUlaunchAttribute attr;
+    memset(&attr, 0, sizeof attr);
+    attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
+    attr.value.programmaticStreamSerializationAllowed = 1;
+    CUlaunchConfig cfg;
+    memset(&cfg, 0, sizeof cfg);
+    cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = shmem;
+    cfg.hStream = dev->stream;
+    cfg.attrs = &attr;
+    cfg.numAttrs = 1;
+    CUresult cr = dev->api->LaunchKernelEx(&cfg, dev->k[which], args, NULL);
+    if (cr != CUDA_SUCCESS) {
+        char what[160];
+        snprintf(what, sizeof what, "cuLaunchKernelEx '%s' grid %u block %u shmem %u", k_names[which], grid, block, shmem);
+        return sm100_fail(dev, what, cr);
+    }
+    dev->launches++;
+    return SM100_OK;
 }
 
 int sm100_rt_sync(sm100_dev_t *dev)
