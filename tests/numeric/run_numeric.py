@@ -11,7 +11,13 @@ element and must then FAIL.
     python tests/numeric/run_numeric.py --backends cpu,sm100 [--full] [--inject] [--update-baseline]
 
 Backends: "cpu" = the CPU checker (oracle/), "sm100" = libbooth_sm100 through its
-C ABI. Exit status 0 when every gating line is ok.
+C ABI, "nvptx" = the PTX the reference compiler's own NVIDIA back end emits for the
+same kernel sources (oracle/_ref/ptx, built by oracle/Makefile), run on the GPU
+through the library's nv_rt_* entry points: the counterpart of the reference
+runner's "nvidia" backend (tests/numeric/run_numeric.py:230-296). It covers vadd,
+saxpy and the chunked sums; for the pricer and the Triton matmul tile the reference
+emits PTX that ptxas rejects, those lines are skipped. Exit status 0 when every
+gating line is ok.
 """
 import argparse
 import json
@@ -119,6 +125,84 @@ class Sm100:
         raise ValueError(name)
 
 
+class NvPtx:
+    """The reference compiler's PTX on the GPU, launched the way the reference's host
+    programs launch (one thread per element, 256-thread blocks; the chunk-sum kernels
+    one block of up to 1024 threads, partial sums combined on the host as the CPU
+    checker combines them)."""
+    name = "nvptx"
+
+    def __init__(self):
+        import ctypes as C
+        self.C = C
+        self.L = L = sm.lib()
+        L.nv_rt_alloc.restype = C.c_uint64
+        L.nv_rt_alloc.argtypes = [C.c_void_p, C.c_size_t]
+        L.nv_rt_free.argtypes = [C.c_void_p, C.c_uint64]
+        L.nv_rt_h2d.argtypes = [C.c_void_p, C.c_uint64, C.c_void_p, C.c_size_t]
+        L.nv_rt_d2h.argtypes = [C.c_void_p, C.c_void_p, C.c_uint64, C.c_size_t]
+        L.nv_rt_load.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p, C.c_void_p]
+        L.nv_rt_launch.argtypes = [C.c_void_p, C.c_void_p] + [C.c_uint32] * 7 + [C.c_void_p]
+        self.dev = (C.c_char * 320)()
+        if L.nv_rt_init(self.dev) != 0:
+            raise RuntimeError("nv_rt_init failed")
+        self.dir = os.path.join(ROOT, "oracle", "_ref", "ptx")
+
+    def close(self):
+        self.L.nv_rt_shut(self.dev)
+
+    def _launch(self, ptx, entry, arrays, scalars, grid, block, out_index):
+        C, L = self.C, self.L
+        path = os.path.join(self.dir, ptx)
+        if not os.path.exists(path):
+            return None
+        k = (C.c_char * 144)()
+        if L.nv_rt_load(self.dev, path.encode(), entry, k) != 0:
+            raise RuntimeError("nv_rt_load %s" % ptx)
+        ptrs = []
+        for arr in arrays:
+            p = L.nv_rt_alloc(self.dev, max(arr.nbytes, 4))
+            L.nv_rt_h2d(self.dev, p, arr.ctypes.data, arr.nbytes)
+            ptrs.append(p)
+        vals = [C.c_uint64(p) for p in ptrs] + scalars
+        args = (C.c_void_p * len(vals))(*[C.cast(C.pointer(v), C.c_void_p) for v in vals])
+        if L.nv_rt_launch(self.dev, k, grid, 1, 1, block, 1, 1, 0, args) != 0 or L.nv_rt_sync(self.dev) != 0:
+            raise RuntimeError("launch of %s" % entry)
+        out = np.empty_like(arrays[out_index])
+        L.nv_rt_d2h(self.dev, out.ctypes.data, ptrs[out_index], out.nbytes)
+        for p in ptrs:
+            L.nv_rt_free(self.dev, p)
+        L.nv_rt_unload(self.dev, k)
+        return out
+
+    def run(self, w, case, seed):
+        C, n, name = self.C, case.get("n", 0), w["name"]
+        if n >= 1 << 28:
+            return None                                  # host-side staging of the whole vector: keep it modest
+        grid = (n + 255) // 256
+        if name == "vadd":
+            x, y = sm.fill_host(n, seed, 0, 0), sm.fill_host(n, seed, 1, 0)
+            return self._launch("vadd.ptx", b"vadd", [x, y, np.empty(n, np.float32)], [C.c_int(n)], grid, 256, 2)
+        if name == "saxpy":
+            x, y = sm.fill_host(n, seed + 1, 0, 0), sm.fill_host(n, seed + 1, 1, 0)
+            return self._launch("saxpy.ptx", b"saxpy", [y, x], [C.c_float(w["alpha"]), C.c_int(n)], grid, 256, 0)
+        if name in ("reduce_i32", "reduce_f32"):
+            threads = min(n, 1024)
+            chunk = n // threads                         # the tail beyond threads * chunk is added on the host
+            kind = name[-3:]
+            v = sm.fill_host(n, seed + 2, 0, 2) if kind == "i32" else sm.fill_host(n, seed + 2, 1, 1)
+            part = self._launch("reduce_chunk_%s.ptx" % kind, ("reduce_chunk_%s" % kind).encode(),
+                                [np.empty(threads, v.dtype), v], [C.c_int(chunk)], 1, threads, 0)
+            if part is None:
+                return None
+            tail = v[threads * chunk:]
+            if kind == "i32":
+                total = part.sum(dtype=np.int64) + tail.sum(dtype=np.int64)
+                return np.array([int(np.int64(total).astype(np.int32))], np.int64)
+            return np.array([float(part.astype(np.float64).sum() + tail.astype(np.float64).sum())], np.float64)
+        return None
+
+
 def gemm_rows4(case):
     if "rows4" not in case:
         return None
@@ -167,6 +251,7 @@ def main():
     names = args.backends.split(",")
     cpu = Cpu()
     gpu = Sm100() if "sm100" in names else None
+    ptx = NvPtx() if "nvptx" in names else None
     failures, measured = [], {}
     for w in man["workloads"]:
         if args.workload and w["name"] != args.workload:
@@ -177,7 +262,10 @@ def main():
             key = key_of(w, case)
             want = cpu.run(w, case, seed)
             for be in names:
-                res = want if be == "cpu" else gpu.run(w, case, seed)
+                res = want if be == "cpu" else gpu.run(w, case, seed) if be == "sm100" else ptx.run(w, case, seed)
+                if res is None:
+                    print("  %-4s %-6s %-40s not produced by this backend" % ("skip", be, key), flush=True)
+                    continue
                 if be == "sm100" and args.inject:
                     res = res.copy()
                     flat = res.reshape(-1)
@@ -212,6 +300,8 @@ def main():
         print("baseline updated:", bl_path)
     if gpu:
         gpu.d.close()
+    if ptx:
+        ptx.close()
     if failures:
         print("FAILED: %d line(s): %s" % (len(failures), ", ".join(failures[:8])))
         return 1

@@ -163,6 +163,31 @@ def test_full_size_vadd_windows_and_sum(sm, dev, oracle_lib):
         dev.free(p)
 
 
+def test_back_to_back_launches_stay_ordered(sm, dev, oracle_lib):
+    """The library launches these kernels so that a launch is set up while the one
+    before it is still finishing. Each step here reads what the previous step wrote
+    (y <- 2.5 x + y sixty times, then out = x + y), at sizes from one block to many
+    waves: any launch that started on stale data would show in the bits."""
+    for n in (1000, (1 << 16) + 3, 1 << 21):
+        x = sm.fill_host(n, 0xB007000C, 0, 0)
+        y = sm.fill_host(n, 0xB007000C, 1, 0)
+        dx, dy, dz = dev.upload(x), dev.upload(y), dev.alloc(n * 4)
+        steps = 60
+        for _ in range(steps):
+            dev.saxpy(dy, dx, 2.5, n)
+        dev.vadd(dx, dy, dz, n)
+        dev.saxpy(dz, dy, -1.0, n)                   # and a kernel reading two freshly written vectors
+        want = y
+        for _ in range(steps):
+            want = oracle_lib.saxpy(want, x, 2.5)
+        out = oracle_lib.vadd(x, want)
+        out = oracle_lib.saxpy(out, want, -1.0)
+        assert mismatches(dev.download(dy, n, np.float32), want) == 0
+        assert mismatches(dev.download(dz, n, np.float32), out) == 0
+        for p in (dx, dy, dz):
+            dev.free(p)
+
+
 def test_host_vector_calls_pipeline_over_chunks(sm, dev, oracle_lib):
     """booth_sm100_saxpy_host / _vadd_host: host vectors longer than two staging
     chunks (16 Mi elements each), pageable and page-locked, bit-exact."""
