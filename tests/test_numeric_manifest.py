@@ -45,3 +45,15 @@ def test_full_size_cases(sm):
     res = run("--backends", "cpu,sm100", "--full")
     assert res.returncode == 0, res.stdout
     assert "saxpy/n=268435456" in res.stdout and "gemm/k=8192,m=8192,n=8192,rows4=16" in res.stdout
+
+
+@pytest.mark.gpu
+def test_reference_ptx_backend_against_cpu_and_baseline(sm):
+    # the counterpart of the reference runner's "nvidia" backend (tests/numeric/run_numeric.py:230-296):
+    # what the reference compiler emits for the GPU, run here, against what it emits for x86-64
+    if not os.path.exists(os.path.join(ROOT, "oracle", "_ref", "ptx", "saxpy.ptx")):
+        pytest.skip("oracle/_ref/ptx was not built (the reference tree was absent at build time)")
+    res = run("--backends", "cpu,nvptx")
+    assert res.returncode == 0, res.stdout
+    assert res.stdout.count(" ok   nvptx") >= 14 and "FAIL" not in res.stdout
+    assert "no baseline" not in res.stdout
