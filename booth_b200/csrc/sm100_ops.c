@@ -100,14 +100,17 @@ int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, l
 
 /* Reductions: 256-thread blocks, eight 16-byte loads per thread in flight. The
  * int32 kernel (32 registers) runs best at 8 blocks per SM (7.3 TB/s at 2^30
- * elements against 7.1 at 6 and 6.6 at 4); the fp32 kernel (54 registers, at most
- * 4 blocks fit an SM) at 4 (7.0 TB/s). BOOTH_SM100_REDUCE_BPSM / _BLOCK override. */
-static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long n, sm100_ptr_t out, int dflt_bpsm)
+ * elements against 7.1 at 6 and 6.6 at 4); the fp32 kernel (62 registers, built
+ * for at most 256 threads per block and 4 blocks per SM) at 3 (7.3 TB/s; 2 to 16
+ * differ by about a percent). BOOTH_SM100_REDUCE_BPSM / _BLOCK override. */
+static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long n, sm100_ptr_t out, int dflt_bpsm,
+                         unsigned max_block)
 {
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
     if (n < 0 || !out || (in & 3)) return bad_arg(dev, "booth_sm100_reduce: bad argument");
-    const unsigned block = (unsigned)env_int("BOOTH_SM100_REDUCE_BLOCK", 256, 32, 1024) & ~31u;
+    unsigned block = (unsigned)env_int("BOOTH_SM100_REDUCE_BLOCK", 256, 32, 1024) & ~31u;
+    if (block > max_block) block = max_block;
     const int bpsm = env_int("BOOTH_SM100_REDUCE_BPSM", dflt_bpsm, 1, 32);
     long long tiles = ((n >> 2) + (long long)block * 8 - 1) / ((long long)block * 8);
     long long g = (long long)dev->sm_count * bpsm;
@@ -122,12 +125,12 @@ static int reduce_common(sm100_dev_t *dev, int which, sm100_ptr_t in, long long 
 
 int booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
 {
-    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out, 8);
+    return reduce_common(dev, SM100_K_REDUCE_I32, in, n, out, 8, 1024);
 }
 
 int booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n, sm100_ptr_t out)
 {
-    return reduce_common(dev, SM100_K_REDUCE_F32, in, n, out, 4);
+    return reduce_common(dev, SM100_K_REDUCE_F32, in, n, out, 3, 256);
 }
 
 int booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
