@@ -184,7 +184,7 @@ int bc_dispatch(bc_device_t *dev, const bc_kernel_t *kern,
     memset(&k, 0, sizeof k);
     k.func = (void *)(uintptr_t)kern->kernel_object;
     k.param_bytes = kern->kernarg_size;
-    snprintf(k.name, sizeof k.name, "bc_dispatch");
+    sm100_func_name(d, k.func, k.name, sizeof k.name);      /* bc_kernel_t carries no name; ask the driver */
     int rc = sm100_rt_launch_packed(d, &k, grid_x, grid_y, grid_z, block_x, block_y, block_z,
                                     0, args, args_size);
     if (rc == SM100_OK) rc = sm100_rt_sync(d);

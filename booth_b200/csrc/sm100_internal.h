@@ -131,6 +131,9 @@ int  sm100_launch_k3(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsi
  * finishing (programmatic stream serialization). */
 int  sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
                                unsigned shmem, void **args);
+/* The kernel's name as the driver knows it, for messages; "kernel" when the driver
+ * cannot say (cuFuncGetName is a CUDA 12.3 entry point). */
+void sm100_func_name(sm100_dev_t *dev, void *func, char *out, size_t n);
 /* Grows the device-owned scratch / GEMM workspace; returns 0 on failure. */
 CUdeviceptr sm100_scratch(sm100_dev_t *dev, size_t bytes);
 CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes);

@@ -388,6 +388,15 @@ int sm100_rt_load(sm100_dev_t *dev, const char *path, const char *name, sm100_ke
     return kern_from_module(dev, mod, 1, name, out);
 }
 
+void sm100_func_name(sm100_dev_t *dev, void *func, char *out, size_t n)
+{
+    const char *name = NULL;
+    if (dev && func && dev->api->FuncGetName && dev->api->FuncGetName(&name, (CUfunction)func) == CUDA_SUCCESS && name && *name)
+        snprintf(out, n, "%s", name);
+    else
+        snprintf(out, n, "kernel");
+}
+
 int sm100_rt_load_builtin(sm100_dev_t *dev, const char *name, sm100_kern_t *out)
 {
     if (!dev || !name || !out) return fail_arg(dev, "sm100_rt_load_builtin: NULL argument");

@@ -172,7 +172,7 @@ L.bc_free(C.byref(d), p); L.bc_device_shutdown(C.byref(d))
     res = subprocess.run([os.sys.executable, "-c", code], cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
                          text=True, timeout=120)
     assert "rc -3" in res.stdout and "rc_ok 0" in res.stdout, res.stdout + res.stderr
-    assert "last dispatch: kernel 'bc_dispatch' grid 1x1x1 block 2048x1x1" in res.stderr
+    assert "last dispatch: kernel 'saxpy' grid 1x1x1 block 2048x1x1" in res.stderr
     assert "24 parameter bytes" in res.stderr and "buffer 'ybuf'" in res.stderr
 
 

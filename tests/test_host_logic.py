@@ -1,0 +1,195 @@
+"""Host-side logic of libbooth_sm100 on a machine without a GPU: which kernels a
+call launches, in which order and geometry, what is copied, and what a failing
+driver call leads to. The driver is tests/fake_driver/fake_cuda.c, a stand-in that
+runs no kernel and computes nothing (device memory is host memory, a launch is a
+line in a log): results are never looked at here, only the host's behaviour.
+Failures are injected on the host, as an error code from the fake of the failing
+call."""
+import os
+import subprocess
+import sys
+
+import pytest
+
+from conftest import ROOT
+
+FAKE_SRC = os.path.join(ROOT, "tests", "fake_driver", "fake_cuda.c")
+CUDA_INC = os.path.join(os.environ.get("CUDA_HOME", "/usr/local/cuda"), "include")
+
+
+@pytest.fixture(scope="module")
+def fake(tmp_path_factory, sm):
+    if not os.path.exists(os.path.join(CUDA_INC, "cuda.h")):
+        pytest.skip("cuda.h not found")
+    out = tmp_path_factory.mktemp("fake_driver") / "libcuda_fake.so"
+    subprocess.run(["gcc", "-std=c99", "-O1", "-shared", "-fPIC", "-I", CUDA_INC, FAKE_SRC, "-o", str(out)], check=True)
+    return str(out)
+
+
+def run(fake, tmp_path, code, **env):
+    log = tmp_path / "driver.log"
+    log.write_text("")
+    full = dict(os.environ, BOOTH_CUDA_LIB=fake, FAKE_CUDA_LOG=str(log), PYTHONPATH=ROOT, **env)
+    res = subprocess.run([sys.executable, "-c", "import booth_b200 as sm\n" + code], cwd=ROOT, env=full,
+                         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    lines = log.read_text().splitlines()
+    launches = []
+    for ln in lines:
+        f = ln.split()
+        if f[0] == "launch":
+            launches.append({"kernel": f[1], "grid": tuple(map(int, f[3:6])), "block": tuple(map(int, f[7:10])),
+                             "shmem": int(f[11]), "overlap": int(f[13]), "packed": int(f[15])})
+    return res, launches, lines
+
+
+def test_streaming_launch_geometry(fake, tmp_path):
+    res, L, _ = run(fake, tmp_path, """
+d = sm.Device(0); x = d.alloc(64); y = d.alloc(64)
+for lg in (30, 28, 27, 24, 10):
+    d.saxpy(y, x, 2.5, 1 << lg)
+d.vadd(x, y, y, 1 << 28); d.vadd(x, y, y, (1 << 24) + 5); d.saxpy(y, x, 1.0, 0)
+d.sync(); d.close()
+""")
+    assert res.returncode == 0, res.stderr
+    assert [l["kernel"] for l in L] == ["saxpy"] * 5 + ["vadd_stream"] * 2          # n = 0 launches nothing
+    assert all(l["block"] == (128, 1, 1) and l["overlap"] == 1 and l["shmem"] == 0 for l in L)
+    # three persistent blocks per SM from 2^28 elements on; below that one 256-chunk tile per block,
+    # at most 128 blocks per SM
+    assert [l["grid"][0] for l in L] == [444, 444, 128 * 148, 8192, 1, 444, 8192]
+
+
+def test_reduction_pricer_and_gemm_launch_sequences(fake, tmp_path):
+    res, L, lines = run(fake, tmp_path, """
+d = sm.Device(0); x = d.alloc(64); y = d.alloc(64); out = d.alloc(64)
+d.reduce_i32(x, 1 << 30, out); d.reduce_f32(x, 1 << 30, out); d.reduce_f32(x, 1000, out)
+d.asian(sm.asian_params(), 0, 1 << 26, out); d.asian(sm.asian_params(precise=1), 0, 1000, out)
+d.gemm(out, x, y, 4096, 4096, 4096)
+d.gemm(out, x, y, 4096, 4096, 4096, b_unchanged=True)
+d.gemm(out, x, y, 8192, 8192, 8192, b_unchanged=True)        # other shape: the flag must be ignored
+d.gemm(out, x, y, 100, 200, 50)
+d.sync(); d.close()
+""")
+    assert res.returncode == 0, res.stderr
+    seq = [(l["kernel"], l["grid"], l["block"][0]) for l in L]
+    assert seq[:5] == [("reduce_sum_i32", (1184, 1, 1), 256), ("reduce_sum_f32", (444, 1, 1), 256),
+                       ("reduce_sum_f32", (1, 1, 1), 256), ("asian_mc", (4736, 1, 1), 256),
+                       ("asian_mc_precise", (4, 1, 1), 256)]
+    g = seq[5:]
+    # 4096^3: split A (one 16-byte chunk per thread), split B (64 x 64 tiles), zero the 34 shared tiles,
+    # then 256 + 34 clusters of two CTAs with 197,632 bytes of dynamic shared memory
+    assert g[:4] == [("gemm_split_a", (16384, 1, 1), 256), ("gemm_split_bt", (64, 64, 1), 256),
+                     ("gemm_zero_tiles", (34, 1, 1), 256), ("gemm_tf32x3_2cta", (580, 1, 1), 320)]
+    assert L[5 + 3]["shmem"] == 197632
+    # same B declared unchanged: no B split
+    assert [k for k, _, _ in g[4:7]] == ["gemm_split_a", "gemm_zero_tiles", "gemm_tf32x3_2cta"]
+    # 8192^3 (1024 tiles = 13 waves + 62: too many leftovers to share): B split again despite the flag
+    assert g[7:10] == [("gemm_split_a", (65536, 1, 1), 256), ("gemm_split_bt", (128, 128, 1), 256),
+                       ("gemm_tf32x3_2cta", (2048, 1, 1), 320)]
+    # 100 x 200 x 50 pads to 128 x 256 x 64: the one-CTA form, one tile
+    assert g[10:] == [("gemm_split_a", (8, 1, 1), 256), ("gemm_split_bt", (4, 1, 1), 256),
+                      ("gemm_tf32x3", (1, 1, 1), 320)]
+    maps = [ln for ln in lines if ln.startswith("tensormap")]
+    assert maps[-4:] == ["tensormap dims 64 128 stride 256 box 32 128"] * 2 + ["tensormap dims 64 256 stride 256 box 32 256"] * 2
+
+
+def test_bc_dispatch_cuts_oversized_argument_blocks_and_is_synchronous(fake, tmp_path):
+    res, L, lines = run(fake, tmp_path, """
+import ctypes as C
+lib = sm.lib(); d = sm.BcDevice(); k = sm.BcKernel()
+assert lib.bc_device_init(C.byref(d)) == 0
+assert lib.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"saxpy", C.byref(k)) == 0
+print("kernarg", k.kernarg_size)
+args = (C.c_char * 42)()                                       # 24 bytes of parameters + 18 hidden ones
+print("rc", lib.bc_dispatch(C.byref(d), C.byref(k), 0, 0, 0, 0, 0, 0, args, 42))
+print("rc", lib.bc_dispatch(C.byref(d), C.byref(k), 7, 3, 2, 33, 3, 1, args, 24))
+lib.bc_device_shutdown(C.byref(d))
+""")
+    assert res.returncode == 0, res.stderr
+    assert "kernarg 24" in res.stdout and res.stdout.count("rc 0") == 2
+    assert L[0]["grid"] == (1, 1, 1) and L[0]["block"] == (1, 1, 1)          # zero dimensions become one
+    assert L[0]["packed"] == 24 and L[1]["packed"] == 24                      # cut to the kernel's own block
+    assert L[1]["grid"] == (7, 3, 2) and L[1]["block"] == (33, 3, 1) and L[1]["overlap"] == 0
+
+
+def test_failed_launch_reports_the_dispatch_and_the_labelled_buffers(fake, tmp_path):
+    res, L, _ = run(fake, tmp_path, """
+import ctypes as C
+lib = sm.lib(); d = sm.BcDevice(); k = sm.BcKernel()
+lib.bc_alloc.restype = C.c_void_p
+lib.bc_trak.argtypes = [C.c_void_p, C.c_void_p, C.c_size_t, C.c_char_p, C.c_int]
+assert lib.bc_device_init(C.byref(d)) == 0
+assert lib.bc_load_kernel(C.byref(d), sm.CUBIN_PATH.encode(), b"saxpy", C.byref(k)) == 0
+p = lib.bc_alloc(C.byref(d), 4096)
+lib.bc_trak(C.byref(d), p, 4096, b"y vector", 0)
+args = (C.c_char * 24)()
+print("first", lib.bc_dispatch(C.byref(d), C.byref(k), 4, 1, 1, 256, 1, 1, args, 24))
+print("second", lib.bc_dispatch(C.byref(d), C.byref(k), 4, 1, 1, 256, 1, 1, args, 24))
+print("third", lib.bc_dispatch(C.byref(d), C.byref(k), 4, 1, 1, 256, 1, 1, args, 24))
+""", FAKE_CUDA_FAIL="cuLaunchKernel:2")
+    assert res.returncode == 0, res.stderr
+    assert "first 0" in res.stdout and "second -3" in res.stdout and "third 0" in res.stdout   # BC_RT_ERR_HSA, then usable again
+    assert len(L) == 2
+    assert "kernel 'saxpy'" in res.stderr and "grid 4x1x1 block 256x1x1" in res.stderr
+    assert "y vector" in res.stderr and "too many resources" in res.stderr
+
+
+def test_allocation_and_wrong_device_failures(fake, tmp_path):
+    res, _, _ = run(fake, tmp_path, """
+import ctypes as C
+lib = sm.lib(); lib.bc_alloc.restype = C.c_void_p
+d = sm.BcDevice(); print("init", lib.bc_device_init(C.byref(d)))
+print("alloc", lib.bc_alloc(C.byref(d), 1 << 20))
+""", FAKE_CUDA_FAIL="cuMemAlloc:2")                    # the first allocation is the library's own scratch
+    assert "init 0" in res.stdout and "alloc None" in res.stdout
+    assert "out of memory" in res.stderr
+    res, _, _ = run(fake, tmp_path, """
+import ctypes as C
+h = C.c_void_p(); print("rc", sm.lib().sm100_rt_init(C.byref(h), 0)); print("rc3", sm.lib().sm100_rt_init(C.byref(h), 3))
+""", FAKE_CUDA_SM_MAJOR="9")
+    assert "rc -4" in res.stdout and "rc3 -4" in res.stdout      # not an sm_100 part; no such ordinal
+    assert "sm_100a code only" in res.stderr
+
+
+def test_offload_abi_copies_in_at_set_and_back_after_the_launch(fake, tmp_path):
+    res, L, lines = run(fake, tmp_path, """
+import ctypes as C, numpy as np
+lib = sm.lib()
+lib.lfortran_gpu_init.restype = C.c_void_p
+lib.lfortran_gpu_load_kernel.restype = C.c_void_p
+lib.lfortran_gpu_load_kernel.argtypes = [C.c_void_p, C.c_char_p, C.c_char_p]
+lib.lfortran_gpu_set_buffer_arg.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t]
+lib.lfortran_gpu_set_scalar_arg.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_size_t]
+lib.lfortran_gpu_launch.argtypes = [C.c_void_p] * 4
+lib.lfortran_gpu_shutdown.argtypes = [C.c_void_p]
+ctx = lib.lfortran_gpu_init()
+k = lib.lfortran_gpu_load_kernel(ctx, None, b"saxpy")
+x = np.ones(1000, np.float32); y = np.ones(500, np.float32)
+a, n = C.c_float(2.0), C.c_int(500)
+lib.lfortran_gpu_set_buffer_arg(k, 0, y.ctypes.data, y.nbytes)
+lib.lfortran_gpu_set_buffer_arg(k, 1, x.ctypes.data, x.nbytes)
+lib.lfortran_gpu_set_scalar_arg(k, 2, C.byref(a), 4); lib.lfortran_gpu_set_scalar_arg(k, 3, C.byref(n), 4)
+lib.lfortran_gpu_launch(ctx, k, (C.c_int * 3)(2, 1, 1), (C.c_int * 3)(256, 1, 1))
+lib.lfortran_gpu_shutdown(ctx)
+print("done")
+""")
+    assert res.returncode == 0 and "done" in res.stdout, res.stderr
+    ops = [ln.split()[0] + " " + ln.split()[1] for ln in lines if not ln.startswith("tensormap")]
+    assert ops == ["h2d 2000", "h2d 4000", "launch saxpy", "d2h 2000", "d2h 4000"]
+    assert L[0]["grid"] == (2, 1, 1) and L[0]["block"] == (256, 1, 1)
+
+
+def test_reference_launcher_api_over_the_fake(fake, tmp_path):
+    res, L, _ = run(fake, tmp_path, """
+import ctypes as C
+lib = sm.lib(); lib.nv_rt_alloc.restype = C.c_uint64
+d = (C.c_char * 320)(); k = (C.c_char * 144)()
+print("init", lib.nv_rt_init(d)); print("load", lib.nv_rt_load(d, sm.CUBIN_PATH.encode(), b"vector_add", k))
+print("missing", lib.nv_rt_load(d, sm.CUBIN_PATH.encode(), b"no_such_kernel", k))
+print("load", lib.nv_rt_load(d, sm.CUBIN_PATH.encode(), b"vector_add", k))
+args = (C.c_void_p * 5)()
+print("launch", lib.nv_rt_launch(d, k, 3, 2, 1, 64, 1, 1, 0, args), lib.nv_rt_sync(d))
+lib.nv_rt_unload(d, k); lib.nv_rt_shut(d); print("after", lib.nv_rt_sync(d))
+""")
+    assert res.returncode == 0, res.stderr
+    assert "init 0" in res.stdout and "missing -6" in res.stdout and "launch 0 0" in res.stdout and "after -3" in res.stdout
+    assert [(l["kernel"], l["grid"], l["block"]) for l in L] == [("vector_add", (3, 2, 1), (64, 1, 1))]
