@@ -116,8 +116,7 @@ CUresult cuFuncGetName(const char **name, CUfunction f) { *name = ((fake_func_t 
 CUresult cuMemAlloc_v2(CUdeviceptr *p, size_t n)
 {
     if (fail_now("cuMemAlloc")) return CUDA_ERROR_OUT_OF_MEMORY;
-    if (n > ((size_t)1 << 28)) n = (size_t)1 << 28;     /* never touched beyond what the tests copy */
-    *p = (CUdeviceptr)(size_t)calloc(1, n ? n : 1);
+    *p = (CUdeviceptr)(size_t)calloc(1, n ? n : 1);         /* large blocks are zero pages until touched */
     return *p ? CUDA_SUCCESS : CUDA_ERROR_OUT_OF_MEMORY;
 }
 CUresult cuMemFree_v2(CUdeviceptr p) { free((void *)(size_t)p); return CUDA_SUCCESS; }

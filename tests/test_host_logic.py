@@ -193,3 +193,37 @@ lib.nv_rt_unload(d, k); lib.nv_rt_shut(d); print("after", lib.nv_rt_sync(d))
     assert res.returncode == 0, res.stderr
     assert "init 0" in res.stdout and "missing -6" in res.stdout and "launch 0 0" in res.stdout and "after -3" in res.stdout
     assert [(l["kernel"], l["grid"], l["block"]) for l in L] == [("vector_add", (3, 2, 1), (64, 1, 1))]
+
+
+def test_host_vector_call_pipelines_chunks_and_leaves_memory_alone(fake, tmp_path):
+    res, L, lines = run(fake, tmp_path, """
+import numpy as np
+d = sm.Device(0)
+n = (20 << 20) + 3                                   # one 16 Mi-element chunk and a ragged second one
+x = np.arange(n, dtype=np.float32); y = np.ones(n, np.float32)
+d.saxpy_host(y.ctypes.data, x.ctypes.data, 2.5, n)
+print("y unchanged by the fake:", bool((y == 1).all()))
+d.vadd_host(x.ctypes.data, y.ctypes.data, y.ctypes.data, 1000)
+d.close()
+""")
+    assert res.returncode == 0, res.stderr
+    assert "y unchanged by the fake: True" in res.stdout          # nothing computes on the CPU
+    ops = [" ".join(ln.split()[:2]) for ln in lines if not ln.startswith("tensormap")]
+    big, rest = 64 << 20, ((4 << 20) + 3) * 4
+    assert ops == ["h2d %d" % big, "h2d %d" % big, "launch saxpy", "d2h %d" % big,
+                   "h2d %d" % rest, "h2d %d" % rest, "launch saxpy", "d2h %d" % rest,
+                   "h2d 4000", "h2d 4000", "launch vadd_stream", "d2h 4000"]
+    assert [l["grid"][0] for l in L] == [8192, 2048, 1]
+
+
+def test_device_ordinal_comes_from_the_environment(fake, tmp_path):
+    res, _, _ = run(fake, tmp_path, """
+import ctypes as C
+lib = sm.lib(); lib.sm100_rt_ordinal.argtypes = [C.c_void_p]
+h = C.c_void_p(); print("rc", lib.sm100_rt_init(C.byref(h), -1), "ordinal", lib.sm100_rt_ordinal(h))
+print("count", lib.sm100_rt_device_count())
+d = sm.BcDevice(); print("bc", lib.bc_device_init(C.byref(d)))
+h2 = C.c_void_p(); print("rc7", lib.sm100_rt_init(C.byref(h2), 7))
+""", FAKE_CUDA_DEVICES="4", BOOTH_DEVICE="2")
+    assert "rc 0 ordinal 2" in res.stdout and "count 4" in res.stdout and "bc 0" in res.stdout and "rc7 -4" in res.stdout
+    assert res.stderr.count("device 2:") == 2
