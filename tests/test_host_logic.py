@@ -26,6 +26,14 @@ def fake(tmp_path_factory, sm):
     return str(out)
 
 
+@pytest.fixture(scope="module")
+def fake_nccl(tmp_path_factory):
+    out = tmp_path_factory.mktemp("fake_nccl") / "libnccl_fake.so"
+    subprocess.run(["gcc", "-std=c99", "-O1", "-shared", "-fPIC", os.path.join(ROOT, "tests", "fake_driver", "fake_nccl.c"),
+                    "-o", str(out)], check=True)
+    return str(out)
+
+
 def run(fake, tmp_path, code, **env):
     log = tmp_path / "driver.log"
     log.write_text("")
@@ -227,3 +235,67 @@ h2 = C.c_void_p(); print("rc7", lib.sm100_rt_init(C.byref(h2), 7))
 """, FAKE_CUDA_DEVICES="4", BOOTH_DEVICE="2")
     assert "rc 0 ordinal 2" in res.stdout and "count 4" in res.stdout and "bc 0" in res.stdout and "rc7 -4" in res.stdout
     assert res.stderr.count("device 2:") == 2
+
+
+def test_collective_host_logic_one_process_per_gpu(fake, fake_nccl, tmp_path):
+    res, _, lines = run(fake, tmp_path, """
+import ctypes as C
+d = sm.Device(0); buf = d.alloc(64)
+uid = sm.Comm.unique_id()
+c = sm.Comm(d, 8, 3, uid)
+c.allreduce_sum(buf, 1, 0)                    # SM100_I32
+c.allreduce_sum(buf, 4, 2)                    # SM100_F64: the pricer's four sums
+c.close(); c.close()
+lib = sm.lib(); h = C.c_void_p()
+print("bad rank", lib.sm100_comm_init_rank(C.byref(h), d.handle, 2, 2, uid))
+d.close()
+""", BOOTH_NCCL_LIB=fake_nccl)
+    assert res.returncode == 0, res.stderr
+    nccl = [ln for ln in lines if ln.startswith("nccl")]
+    assert nccl == ["nccl init_rank 3 of 8", "nccl allreduce rank 3 count 1 dtype 2 op 0 inplace 1",
+                    "nccl allreduce rank 3 count 4 dtype 8 op 0 inplace 1", "nccl destroy rank 3"]
+    assert "bad rank -7" in res.stdout
+
+
+def test_collective_host_logic_one_process_many_gpus_and_a_failing_peer(fake, fake_nccl, tmp_path):
+    code = """
+import ctypes as C
+lib = sm.lib()
+devs = (C.c_void_p * 4)()
+for i in range(4):
+    h = C.c_void_p(); assert lib.sm100_rt_init(C.byref(h), i) == 0; devs[i] = h
+lib.sm100_rt_alloc.restype = C.c_uint64; lib.sm100_rt_alloc.argtypes = [C.c_void_p, C.c_size_t]
+lib.sm100_comm_allreduce_sum_dev.argtypes = [C.c_void_p, C.c_int, C.c_uint64, C.c_size_t, C.c_int]
+lib.sm100_comm_allreduce_sum.argtypes = [C.c_void_p, C.c_uint64, C.c_size_t, C.c_int]
+bufs = [lib.sm100_rt_alloc(devs[i], 64) for i in range(4)]
+comm = C.c_void_p(); print("init_all", lib.sm100_comm_init_all(C.byref(comm), devs, 4))
+print("wrong form", lib.sm100_comm_allreduce_sum(comm, bufs[0], 1, 1))
+for step in range(3):
+    print("begin", lib.sm100_comm_group_begin())
+    rcs = [lib.sm100_comm_allreduce_sum_dev(comm, i, bufs[i], 1, 1) for i in range(4)]
+    print("step", step, rcs, "end", lib.sm100_comm_group_end())
+print("bad index", lib.sm100_comm_allreduce_sum_dev(comm, 4, bufs[0], 1, 1))
+lib.sm100_comm_destroy(comm)
+"""
+    res, _, lines = run(fake, tmp_path, code, BOOTH_NCCL_LIB=fake_nccl, FAKE_CUDA_DEVICES="4", FAKE_NCCL_FAIL="ncclAllReduce:6")
+    assert res.returncode == 0, res.stderr
+    assert "init_all 0" in res.stdout and "wrong form -7" in res.stdout and "bad index -7" in res.stdout
+    # the sixth all-reduce (step 1, device 1) fails: reported as the NCCL status, with the library's text,
+    # and the process carries on; nothing hangs, nothing is retried behind the caller's back
+    assert "step 0 [0, 0, 0, 0] end 0" in res.stdout and "step 1 [0, -8, 0, 0] end 0" in res.stdout
+    assert "step 2 [0, 0, 0, 0] end 0" in res.stdout
+    assert "ncclAllReduce: fake: unhandled system error" in res.stderr
+    nccl = [ln for ln in lines if ln.startswith("nccl")]
+    assert nccl[0] == "nccl init_all 4 devices, first ordinal 0"
+    assert nccl[1:7] == ["nccl group_start"] + ["nccl allreduce rank %d count 1 dtype 7 op 0 inplace 1" % i for i in range(4)] + ["nccl group_end"]
+    assert nccl[-4:] == ["nccl destroy rank %d" % i for i in range(4)]
+
+
+def test_missing_collective_library_is_an_error(fake, tmp_path):
+    res, _, _ = run(fake, tmp_path, """
+try:
+    sm.Comm.unique_id(); print("got an id")
+except sm.Sm100Error as e:
+    print("error", e.status if hasattr(e, "status") else e)
+""", BOOTH_NCCL_LIB="/nonexistent/libnccl.so.2")
+    assert "got an id" not in res.stdout and "error" in res.stdout
