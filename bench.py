@@ -328,7 +328,9 @@ def run_ours(args):
         "config": {"workload": "saxpy y=2.5*x+y, N=2^%d fp32 per GPU, unfused mul+add, x,y~U[-1,1) Philox-seeded"
                                % args.log2n,
                    "bytes_per_element": 12, "sharding": "contiguous ranges, no data-path collective",
-                   "cache": "inputs (8 GiB per GPU) exceed the 126 MB L2; no flush needed"},
+                   "cache": ("inputs (%.3g GiB per GPU) exceed the 126 MB L2; no flush needed" % (8.0 * n / 2 ** 30)
+                             if 8 * n > (256 << 20) else
+                             "inputs (%.3g MiB per GPU) fit the 126 MB L2: not an HBM figure" % (8.0 * n / 2 ** 20))},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         "roofline": head_roof,
         "workloads": workloads,

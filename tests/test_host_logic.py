@@ -299,3 +299,50 @@ except sm.Sm100Error as e:
     print("error", e.status if hasattr(e, "status") else e)
 """, BOOTH_NCCL_LIB="/nonexistent/libnccl.so.2")
     assert "got an id" not in res.stdout and "error" in res.stdout
+
+
+def test_bench_line_keeps_its_contract_over_the_fake(fake, fake_nccl, tmp_path):
+    """bench.py end to end at toy sizes over the fake driver: the figures mean nothing
+    (the fake's clock says 1 ms per timed region), the shape of the one JSON line on
+    stdout is what is checked."""
+    import json
+    env = dict(os.environ, BOOTH_CUDA_LIB=fake, BOOTH_NCCL_LIB=fake_nccl, PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--log2n", "16", "--log2paths", "10", "--gemm-sizes", "256",
+                          "--steps", "4", "--warmup", "3", "--cpu-seconds", "0.05"], cwd=ROOT, env=env,
+                         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = [ln for ln in res.stdout.splitlines() if ln.strip()]
+    assert len(out) == 1, out                                   # exactly one line on stdout
+    j = json.loads(out[0])
+    for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "e2e", "gpu_launches", "clocks", "roofline", "cpu_baseline"):
+        assert key in j, key
+    assert j["n_gpus"] == 1 and j["steps"] == 4 and j["warmup"] == 3 and j["gpu_launches"] == 4
+    assert j["vs_baseline"] is None and j["dtype"] == "f32" and j["scaling"] == "weak" and j["higher_is_better"] is True
+    assert set(j["roofline"]) >= {"bound", "achieved", "peak", "unit", "frac", "traffic"}
+    assert set(j["e2e"]) >= {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"}
+    assert j["e2e"]["h2d_bytes_per_step"] == 2 * 4 * (1 << 16) and j["e2e"]["d2h_bytes_per_step"] == 4 * (1 << 16)
+    assert set(j["cpu_baseline"]) >= {"value", "unit", "cores", "kind", "sample"}
+    assert "workload" in j["config"] and "model" not in j["config"]
+    names = [w["name"] for w in j["workloads"]]
+    assert any(n.startswith("gemm") for n in names) and any(n.startswith("asian") for n in names)
+
+
+def test_reference_arm_line_needs_no_gpu(tmp_path):
+    """bench.py --impl reference times the reference compiler's x86-64 objects (or
+    their C restatement) on the host cores: same metric and config as the GPU arm,
+    one JSON line, no driver touched."""
+    import json
+    env = dict(os.environ, BOOTH_CUDA_LIB="/nonexistent/libcuda.so.1", PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+                         cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
+    assert res.returncode == 0, res.stderr[-2000:]
+    out = [ln for ln in res.stdout.splitlines() if ln.strip()]
+    assert len(out) == 1
+    j = json.loads(out[0])
+    assert j["impl"] == "reference" and j["metric"] == "saxpy_hbm_gbs" and j["unit"] == "GB/s" and j["n_gpus"] == 1
+    assert j["higher_is_better"] is True and j["value"] > 0
+    assert j["cpu_baseline"]["kind"] in ("reference", "port") and j["cpu_baseline"]["cores"] >= 1
+    assert j["cpu_baseline"]["value"] == j["value"] == j["e2e"]["value"]
+    assert j["e2e"]["h2d_bytes_per_step"] == 0 and j["e2e"]["d2h_bytes_per_step"] == 0
+    assert "N=2^30" in j["config"]["workload"]
