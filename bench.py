@@ -406,7 +406,8 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps):
     ranks.barrier()
     dev.hostfree(hx); dev.hostfree(hy)
     return {"value": 12.0 * n * ranks.world * steps / dt / 1e9, "unit": "GB/s", "steps": steps,
-            "h2d_bytes_per_step": 2 * nbytes, "d2h_bytes_per_step": nbytes,
+            "h2d_bytes_per_step": 2 * nbytes * ranks.world, "d2h_bytes_per_step": nbytes * ranks.world,
+            "bytes_scope": "whole job (all GPUs), like value",
             "api": "booth_sm100_saxpy_host on pinned host vectors: 16 Mi-element chunks, H2D / saxpy / D2H pipelined "
                    "on two streams; returns with y in host memory",
             "launcher_api": launcher}

@@ -346,3 +346,26 @@ def test_reference_arm_line_needs_no_gpu(tmp_path):
     assert j["cpu_baseline"]["value"] == j["value"] == j["e2e"]["value"]
     assert j["e2e"]["h2d_bytes_per_step"] == 0 and j["e2e"]["d2h_bytes_per_step"] == 0
     assert "N=2^30" in j["config"]["workload"]
+
+
+def test_two_rank_bench_path_over_the_fakes(fake, fake_nccl, tmp_path):
+    """The launch the driver uses for N > 1 (torchrun, one rank per GPU), on the CPU:
+    two ranks on two fake devices, the NCCL id travelling through the gloo group,
+    rank 0 alone printing the line, whole-job figures."""
+    import json
+    env = dict(os.environ, BOOTH_CUDA_LIB=fake, BOOTH_NCCL_LIB=fake_nccl, FAKE_CUDA_DEVICES="2", PYTHONPATH=ROOT,
+               FAKE_CUDA_LOG=str(tmp_path / "driver.log"))
+    res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                          "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "bench.py"),
+                          "--gpus", "2", "--log2n", "16", "--log2paths", "10", "--gemm-sizes", "256", "--steps", "3",
+                          "--warmup", "3", "--no-cpu-baseline"], cwd=ROOT, env=env, stdout=subprocess.PIPE,
+                         stderr=subprocess.PIPE, text=True, timeout=900)
+    assert res.returncode == 0, res.stderr[-3000:]
+    out = [ln for ln in res.stdout.splitlines() if ln.strip().startswith("{")]
+    assert len(out) == 1
+    j = json.loads(out[0])
+    assert j["n_gpus"] == 2 and j["scaling"] == "weak" and j["gpu_launches"] == 3
+    assert j["e2e"]["h2d_bytes_per_step"] == 2 * 2 * 4 * (1 << 16)            # both ranks' vectors
+    log = (tmp_path / "driver.log").read_text()
+    assert "nccl init_rank 0 of 2" in log and "nccl init_rank 1 of 2" in log
+    assert log.count("nccl allreduce") >= 2 * 2                                # sums and prices, on both ranks
