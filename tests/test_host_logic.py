@@ -369,3 +369,19 @@ def test_two_rank_bench_path_over_the_fakes(fake, fake_nccl, tmp_path):
     log = (tmp_path / "driver.log").read_text()
     assert "nccl init_rank 0 of 2" in log and "nccl init_rank 1 of 2" in log
     assert log.count("nccl allreduce") >= 2 * 2                                # sums and prices, on both ranks
+
+
+def test_nothing_is_computed_on_the_host(fake, tmp_path):
+    """The reference's own example programs, relinked against the library, check
+    their results themselves. Over the fake driver, where no kernel runs, they must
+    report mismatches: the library has no path that computes on the CPU."""
+    ex = os.path.join(ROOT, "build", "examples")
+    if not os.path.exists(os.path.join(ex, "launch_saxpy")):
+        pytest.skip("build/examples was not built (the reference tree was absent at build time)")
+    env = dict(os.environ, BOOTH_CUDA_LIB=fake)
+    res = subprocess.run([os.path.join(ex, "launch_saxpy"), os.path.join(ROOT, "booth_b200", "lib", "booth_sm100.cubin")],
+                         env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=60)
+    assert "FAIL: 1023/1024 mismatches" in res.stdout                 # element 0 is x[0] = 0: y unchanged is right there
+    res = subprocess.run([os.path.join(ex, "cpu_launch_vadd")], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
+                         text=True, timeout=60)
+    assert "MISMATCH" in res.stdout and "OK" not in res.stdout.replace("MISMATCH", "")
