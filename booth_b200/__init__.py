@@ -19,8 +19,9 @@ CUBIN_PATH = os.path.join(_HERE, "lib", "booth_sm100.cubin")
 INCLUDE_DIR = os.path.join(os.path.dirname(_HERE), "include")
 
 OK, ERR_DL, ERR_SYM, ERR_CUDA, ERR_NO_GPU, ERR_IO, ERR_KERN, ERR_ARG, ERR_NCCL = 0, -1, -2, -3, -4, -5, -6, -7, -8
-FILL_F32_PM1, FILL_F32_01, FILL_I32_1000 = 0, 1, 2
+FILL_F32_PM1, FILL_F32_01, FILL_I32_1000, FILL_U32_RAW = 0, 1, 2, 3
 I32, F32, F64 = 0, 1, 2
+GEMM_B_UNCHANGED, GEMM_TEST_SILENT_PRODUCER = 1, 0x80000000
 COMM_ID_BYTES = 128
 
 _ptr = C.c_ulonglong
@@ -91,6 +92,7 @@ _SIGNATURES = {
     # layer 2
     "booth_sm100_fill": (C.c_int, [_dev, _ptr, C.c_longlong, C.c_longlong, C.c_uint32, C.c_uint32, C.c_int]),
     "booth_sm100_fill_host": (None, [C.c_void_p, C.c_longlong, C.c_longlong, C.c_uint32, C.c_uint32, C.c_int, C.c_int]),
+    "booth_sm100_philox4x32_10": (None, [C.c_void_p, C.c_void_p, C.c_void_p]),
     "booth_sm100_vadd": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_longlong]),
     "booth_sm100_saxpy": (C.c_int, [_dev, _ptr, _ptr, C.c_float, C.c_longlong]),
     "booth_sm100_vadd_host": (C.c_int, [_dev, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong]),
@@ -100,6 +102,7 @@ _SIGNATURES = {
     "booth_sm100_reduce_f32_noalloc": (C.c_int, [_ptr, C.c_longlong, _ptr, C.c_void_p]),
     "booth_sm100_gemm": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_int, C.c_int, C.c_int]),
     "booth_sm100_gemm_ex": (C.c_int, [_dev, _ptr, _ptr, _ptr, C.c_int, C.c_int, C.c_int, C.c_uint]),
+    "booth_sm100_gemm_wait_limit": (C.c_int, [_dev, C.c_uint]),
     "booth_sm100_asian": (C.c_int, [_dev, C.POINTER(AsianParams), C.c_longlong, C.c_longlong, _ptr]),
     "booth_sm100_asian_paths": (C.c_int, [_dev, C.POINTER(AsianParams), C.c_longlong, C.c_longlong, _ptr, _ptr]),
     # layer 3
@@ -127,6 +130,7 @@ _SIGNATURES = {
     "matmul": (None, [C.c_void_p] * 3 + [C.c_int] * 7),
     "matmul_k": (None, [C.c_void_p] * 3 + [C.c_int] * 8),
     "saxpy": (None, [C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int]),
+    "vadd": (None, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int]),
 }
 
 _lib = None
@@ -278,11 +282,15 @@ class Device:
     def reduce_f32(self, inp, n, out):
         self._ck("booth_sm100_reduce_f32", lib().booth_sm100_reduce_f32(self._h, inp, n, out))
 
-    def gemm(self, c, a, b, M, N, K, b_unchanged=False):
-        if b_unchanged:
-            self._ck("booth_sm100_gemm_ex", lib().booth_sm100_gemm_ex(self._h, c, a, b, M, N, K, 1))
+    def gemm(self, c, a, b, M, N, K, b_unchanged=False, flags=0):
+        flags |= GEMM_B_UNCHANGED if b_unchanged else 0
+        if flags:
+            self._ck("booth_sm100_gemm_ex", lib().booth_sm100_gemm_ex(self._h, c, a, b, M, N, K, flags))
         else:
             self._ck("booth_sm100_gemm", lib().booth_sm100_gemm(self._h, c, a, b, M, N, K))
+
+    def gemm_wait_limit(self, ms):
+        self._ck("booth_sm100_gemm_wait_limit", lib().booth_sm100_gemm_wait_limit(self._h, ms))
 
     def asian(self, params, path0, npaths, out):
         self._ck("booth_sm100_asian", lib().booth_sm100_asian(self._h, C.byref(params), path0, npaths, out))
@@ -323,7 +331,7 @@ class Comm:
 
 def fill_host(n, seed, stream, kind, first=0, threads=8):
     """The seeded input stream, generated on the host (same bits as Device.fill)."""
-    out = np.empty(n, dtype=np.int32 if kind == FILL_I32_1000 else np.float32)
+    out = np.empty(n, dtype={FILL_I32_1000: np.int32, FILL_U32_RAW: np.uint32}.get(kind, np.float32))
     lib().booth_sm100_fill_host(_addr(out), first, n, seed, stream, kind, threads)
     return out
 

@@ -12,10 +12,11 @@
 // whole tiles (Mp, Np, Kp), the contraction runs on the padded planes (K here is
 // Kp), and the epilogue stores only the M x N that exist.
 //
-// Three kernels:
-//   gemm_split_a    A[M,K]  -> A_hi, A_lo [Mp,Kp]          (elementwise, streaming)
-//   gemm_split_bt   B[K,N]  -> Bt_hi, Bt_lo [Np,Kp]        (split + transpose through
-//                   shared memory, so both MMA operands are K-major)
+// Two launches per GEMM:
+//   gemm_prepass    A[M,K]  -> A_hi, A_lo [Mp,Kp]          (elementwise, streaming)
+//                   B[K,N]  -> Bt_hi, Bt_lo [Np,Kp]        (split + transpose through
+//                   shared memory, so both MMA operands are K-major), and zeros in
+//                   the tiles of C that two clusters add into
 //   gemm_tf32x3     one 128 x BN tile of C per CTA:
 //       warp 0, one lane : TMA producer. cp.async.bulk.tensor (128-byte swizzle, no
 //                          multicast) brings the four operand tiles of a 32-wide
@@ -135,16 +136,19 @@ __device__ __forceinline__ float to_tf32(float x)
 
 }  // namespace gemm
 
+namespace gemm {
+
 // A[M,K] row-major -> hi/lo planes [Mp,Kp] (Mp >= M, Kp >= K, Kp % 4 == 0), zero in
 // the padding: hi = tf32(a), lo = tf32(a - hi). Without padding and with K % 4 == 0
-// the planes are walked as one flat array of 16-byte chunks.
-extern "C" __global__ void gemm_split_a(const float *__restrict__ a, float4 *__restrict__ hi,
-                                        float4 *__restrict__ lo, int M, int K, int Mp, int Kp)
+// the planes are walked as one flat array of 16-byte chunks. Block `blk` of
+// `nblk` blocks of 256 threads.
+__device__ __forceinline__ void split_a_part(const float *__restrict__ a, float4 *__restrict__ hi, float4 *__restrict__ lo,
+                                             int M, int K, int Mp, int Kp, unsigned blk, unsigned nblk)
 {
-    const long long T = (long long)gridDim.x * blockDim.x;
+    const long long T = (long long)nblk * 256;
     const long long kp4 = Kp >> 2, total = (long long)Mp * kp4;
     const bool flat = M == Mp && K == Kp && (((uintptr_t)a) & 15) == 0;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += T) {
+    for (long long i = (long long)blk * 256 + threadIdx.x; i < total; i += T) {
         float4 v;
         if (flat) {
             v = __ldcs(reinterpret_cast<const float4 *>(a) + i);
@@ -158,25 +162,24 @@ extern "C" __global__ void gemm_split_a(const float *__restrict__ a, float4 *__r
             v.w = (row < M && k + 3 < K) ? src[3] : 0.0f;
         }
         float4 h, l;
-        h.x = gemm::to_tf32(v.x); l.x = gemm::to_tf32(v.x - h.x);
-        h.y = gemm::to_tf32(v.y); l.y = gemm::to_tf32(v.y - h.y);
-        h.z = gemm::to_tf32(v.z); l.z = gemm::to_tf32(v.z - h.z);
-        h.w = gemm::to_tf32(v.w); l.w = gemm::to_tf32(v.w - h.w);
+        h.x = to_tf32(v.x); l.x = to_tf32(v.x - h.x);
+        h.y = to_tf32(v.y); l.y = to_tf32(v.y - h.y);
+        h.z = to_tf32(v.z); l.z = to_tf32(v.z - h.z);
+        h.w = to_tf32(v.w); l.w = to_tf32(v.w - h.w);
         hi[i] = h;
         lo[i] = l;
     }
 }
 
 // B[K,N] row-major -> hi/lo planes of B^T, [Np,Kp] row-major, zero in the padding.
-// 64x64 tiles through shared memory (padded against bank conflicts), 256 threads,
-// grid (Np/64, ceil(Kp/64)): rows of B are read in 256-byte runs (16-byte loads
-// when N and the pointer allow), rows of B^T written in 256-byte runs of 16-byte
-// stores.
-extern "C" __global__ void __launch_bounds__(256)
-gemm_split_bt(const float *__restrict__ b, float *__restrict__ hi, float *__restrict__ lo, int K, int N, int Kp)
+// One 64x64 tile (tile column bx of B^T rows, tile row by of K) through shared
+// memory (padded against bank conflicts), 256 threads: rows of B are read in
+// 256-byte runs (16-byte loads when N and the pointer allow), rows of B^T written
+// in 256-byte runs of 16-byte stores.
+__device__ __forceinline__ void split_bt_part(const float *__restrict__ b, float *__restrict__ hi, float *__restrict__ lo,
+                                              int K, int N, int Kp, float (*tile)[65], int bx, int by)
 {
-    __shared__ float tile[64][65];            // [k][n]
-    const int n0 = blockIdx.x * 64, k0 = blockIdx.y * 64;
+    const int n0 = bx * 64, k0 = by * 64;
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;          // 16 x 16
     const bool vec = (N & 3) == 0 && (((uintptr_t)b) & 15) == 0;
 #pragma unroll
@@ -203,17 +206,16 @@ gemm_split_bt(const float *__restrict__ b, float *__restrict__ hi, float *__rest
         if (k >= Kp) continue;
         float4 h, l;
         const float v0 = tile[4 * tx + 0][nl], v1 = tile[4 * tx + 1][nl], v2 = tile[4 * tx + 2][nl], v3 = tile[4 * tx + 3][nl];
-        h.x = gemm::to_tf32(v0); l.x = gemm::to_tf32(v0 - h.x);
-        h.y = gemm::to_tf32(v1); l.y = gemm::to_tf32(v1 - h.y);
-        h.z = gemm::to_tf32(v2); l.z = gemm::to_tf32(v2 - h.z);
-        h.w = gemm::to_tf32(v3); l.w = gemm::to_tf32(v3 - h.w);
+        h.x = to_tf32(v0); l.x = to_tf32(v0 - h.x);
+        h.y = to_tf32(v1); l.y = to_tf32(v1 - h.y);
+        h.z = to_tf32(v2); l.z = to_tf32(v2 - h.z);
+        h.w = to_tf32(v3); l.w = to_tf32(v3 - h.w);
         const long long o = (long long)(n0 + nl) * Kp + k;
         *reinterpret_cast<float4 *>(hi + o) = h;
         *reinterpret_cast<float4 *>(lo + o) = l;
     }
 }
 
-namespace gemm {
 // Pair-tile index -> (tile row, tile column). Tiles are numbered in groups of
 // eight tile rows, column by column inside a group, so the ~74 tiles that run at
 // the same time form a block about 8 tall and 9 wide and share their A and B
@@ -229,19 +231,55 @@ __device__ __forceinline__ void pair_tile_coords(int tile, int tiles_m, int tile
     tm = first_m + in_group % rows;
     tn = in_group / rows;
 }
-}  // namespace gemm
 
-// Zeroes the 256 x 256 tiles of C numbered tile_from, tile_from + 1, ... (one
-// block per tile, numbering of pair_tile_coords), clipped to M x N: the tiles two
-// clusters will add their halves of K into.
-extern "C" __global__ void gemm_zero_tiles(float *__restrict__ c, int M, int N, int tiles_n, int tile_from)
+// Zeroes one 256 x 256 tile of C (numbering of pair_tile_coords), clipped to
+// M x N: a tile two clusters will add their halves of K into.
+__device__ __forceinline__ void zero_tile_part(float *__restrict__ c, int M, int N, int tiles_n, int tile)
 {
     int tm, tn;
-    gemm::pair_tile_coords(tile_from + blockIdx.x, (M + 255) / 256, tiles_n, tm, tn);
+    pair_tile_coords(tile, (M + 255) / 256, tiles_n, tm, tn);
     const int r0 = tm * 256, c0 = tn * 256;
-    for (int i = threadIdx.x; i < 256 * 256; i += blockDim.x) {
-        const int r = r0 + (i >> 8), col = c0 + (i & 255);
-        if (r < M && col < N) c[(long long)r * N + col] = 0.0f;
+    if ((N & 3) == 0 && (((uintptr_t)c) & 15) == 0) {
+        for (int i = threadIdx.x; i < 256 * 64; i += 256) {
+            const int r = r0 + (i >> 6), col = c0 + ((i & 63) << 2);
+            if (r < M && col < N) *reinterpret_cast<float4 *>(c + (long long)r * N + col) = make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    } else {
+        for (int i = threadIdx.x; i < 256 * 256; i += 256) {
+            const int r = r0 + (i >> 8), col = c0 + (i & 255);
+            if (r < M && col < N) c[(long long)r * N + col] = 0.0f;
+        }
+    }
+}
+}  // namespace gemm
+
+// Everything the contraction needs beforehand, in ONE launch of 256-thread blocks
+// (grid = a_blocks + b_blocks + n_zero):
+//   blocks [0, a_blocks)                     split A into its hi/lo planes;
+//   blocks [a_blocks, a_blocks + b_blocks)   split and transpose 64 x 64 tiles of B
+//                                            (b_blocks = 0 when the planes of B are kept);
+//   the last n_zero blocks                   zero the tiles of C that two clusters share.
+// The parts are independent and all bound by HBM, so they stream side by side.
+// Launched with programmatic stream serialization: the grid is set up while the
+// previous kernel on the stream drains, waits for that kernel's memory (it may
+// still be reading the planes, or writing a and b), then lets the contraction
+// behind it do the same.
+extern "C" __global__ void __launch_bounds__(256)
+gemm_prepass(const float *__restrict__ a, float4 *__restrict__ a_hi, float4 *__restrict__ a_lo, int M, int K, int Mp, int Kp,
+             const float *__restrict__ b, float *__restrict__ b_hi, float *__restrict__ b_lo, int N, int Np,
+             float *__restrict__ c, int tiles_n, int tile_from, unsigned a_blocks, unsigned b_blocks)
+{
+    __shared__ float tile[64][65];            // [k][n], used by the B part
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
+    const unsigned blk = blockIdx.x;
+    if (blk < a_blocks) {
+        gemm::split_a_part(a, a_hi, a_lo, M, K, Mp, Kp, blk, a_blocks);
+    } else if (blk < a_blocks + b_blocks) {
+        const unsigned t = blk - a_blocks, nbx = (unsigned)Np / 64u;
+        gemm::split_bt_part(b, b_hi, b_lo, K, N, Kp, tile, (int)(t % nbx), (int)(t / nbx));
+    } else {
+        gemm::zero_tile_part(c, M, N, tiles_n, tile_from + (int)(blk - a_blocks - b_blocks));
     }
 }
 
@@ -329,6 +367,11 @@ __device__ __forceinline__ void gemm_tile(const CUtensorMap *map_a_hi, const CUt
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
+    // Everything above touched only this CTA's own shared and tensor memory, so
+    // under programmatic stream serialization it overlaps the tail of the kernel
+    // before (the operand split). The planes and C are touched only from here on.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
 
     if (warp == 0) {
         // ---- TMA producer (one lane) ----
@@ -573,6 +616,8 @@ __device__ __forceinline__ void gemm_pair_tile(const CUtensorMap &map_a_hi, cons
     cluster_sync_all();     // both CTAs' barriers are initialised before anyone signals them
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem = s_tmem;
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // see the one-CTA form
+    asm volatile("griddepcontrol.launch_dependents;");
 
     if (warp == 0) {
         // ---- TMA producer, one lane in each CTA; completions count on the leader's barrier ----

@@ -205,6 +205,7 @@ extern "C" __global__ void __maxnreg__(48) saxpy(float *y, const float *x, float
 __device__ __forceinline__ uint32_t fill_value(uint32_t x, int kind)
 {
     if (kind == 2) return (uint32_t)((int)(x % 2001u) - 1000);
+    if (kind == 3) return x;                                        // the raw word
     const float u = (float)(x >> 8) * 5.9604644775390625e-8f;       // exact, [0,1)
     const float v = kind == 0 ? __fadd_rn(__fmul_rn(2.0f, u), -1.0f) : u;
     return __float_as_uint(v);
@@ -229,4 +230,16 @@ extern "C" __global__ void fill_philox(uint32_t *dst, long long first, long long
             if (j >= 0 && j < n) dst[j] = fill_value(v[l], kind);
         }
     }
+}
+
+// Raw Philox4x32-10 output for a caller-given counter and key: thread t of the
+// launch writes the four words of the block with counter (c0 + t, c1, c2, c3) to
+// out[4t .. 4t+3]. Looked up by name; it exists so that the generator can be
+// checked on the device against the known-answer vectors published with Random123.
+extern "C" __global__ void philox_words(uint32_t *out, uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3,
+                                        uint32_t k0, uint32_t k1)
+{
+    const unsigned t = flat_bid() * flat_bdim() + flat_tid();
+    const Philox4 r = philox4x32_10(c0 + t, c1, c2, c3, k0, k1);
+    out[4 * t + 0] = r.x; out[4 * t + 1] = r.y; out[4 * t + 2] = r.z; out[4 * t + 3] = r.w;
 }

@@ -14,11 +14,13 @@
 //     on which this entry point is used holds it from first use until exit;
 //   * the input is cut into segments of 262,144 elements, one block and one
 //     scratch slot per segment, 4,096 slots: n above 2^30 is refused;
-//   * the first call on a device looks the array's device address up
+//   * every call looks the array's device address up for the current device
 //     (cudaGetSymbolAddress; the array's name in host code is only a stand-in,
-//     not an address a kernel could use), which makes the runtime load this
-//     library's device code on that device. Make that first call before any
-//     stream capture begins;
+//     not an address a kernel could use). The first such call on a device makes
+//     the runtime load this library's device code there: make that first call
+//     before any stream capture begins. Later calls are a table look-up, and
+//     asking each time keeps the address right after the application has reset
+//     the device;
 //   * all calls share the one array and it keeps what the previous call left,
 //     so each call first clears the arrival counter on the caller's stream.
 //     Two calls that may run on the GPU at the same time (different streams,
@@ -26,11 +28,15 @@
 //   * nothing here calls cudaMalloc, cudaFree or a library routine that
 //     allocates. The result is written to memory the caller passes.
 //
-// Because the segment size is fixed, the sum is bit-identical on any GPU and for
-// any SM count, which the grid-sized booth_sm100_reduce_f32 does not promise.
+// Because the segment size is fixed, the sum does not depend on the GPU or its SM
+// count (the grid-sized booth_sm100_reduce_f32 does not promise that): the same
+// input at the same 16-byte alignment gives the same bits everywhere. An input
+// that is only 4-byte aligned is added up in a different order (scalar loads)
+// and may differ from the aligned result in the last bits.
+// in must be 4-byte aligned, out 8-byte aligned (it receives a double); both are
+// checked here, before any GPU work, because the device would fault on them.
 #include <cstdint>
 #include <cstdio>
-#include <mutex>
 #include <cuda_runtime.h>
 
 #include "booth_sm100.h"
@@ -42,7 +48,6 @@ constexpr long long NOALLOC_SEGMENT = 1ll << 18;       // elements per block
 constexpr int NOALLOC_SLOTS = 4096;                     // segment sums the scratch holds
 constexpr long long NOALLOC_MAX_N = NOALLOC_SEGMENT * NOALLOC_SLOTS;
 constexpr size_t NOALLOC_HEADER = 256;                  // arrival counter lives here
-constexpr int NOALLOC_MAX_DEVICES = 64;
 
 // [0,256): arrival counter (first 4 bytes). [256, ...): one double per segment.
 static __device__ __align__(256) unsigned char g_scratch[NOALLOC_HEADER + NOALLOC_SLOTS * sizeof(double)];
@@ -123,9 +128,6 @@ reduce_f32_segments(const float *__restrict__ in, long long n, unsigned char *sc
     if (threadIdx.x == 0) { *out = v; *ticket = 0u; }
 }
 
-std::mutex g_setup_mutex;
-unsigned char *g_scratch_addr[NOALLOC_MAX_DEVICES];     // device address of g_scratch, per device
-
 int fail(const char *what, cudaError_t e)
 {
     std::fprintf(stderr, "sm100_rt: booth_sm100_reduce_f32_noalloc: %s: %s\n", what, cudaGetErrorString(e));
@@ -136,8 +138,9 @@ int fail(const char *what, cudaError_t e)
 
 extern "C" int booth_sm100_reduce_f32_noalloc(sm100_ptr_t in, long long n, sm100_ptr_t out, void *stream)
 {
-    if (!out || n < 0 || (n > 0 && !in) || (in & 3)) {
-        std::fprintf(stderr, "sm100_rt: booth_sm100_reduce_f32_noalloc: bad argument\n");
+    if (!out || (out & 7) || n < 0 || (n > 0 && !in) || (in & 3)) {
+        std::fprintf(stderr, "sm100_rt: booth_sm100_reduce_f32_noalloc: bad argument (in: 4-byte aligned, "
+                     "non-NULL when n > 0; out: 8-byte aligned)\n");
         return SM100_ERR_ARG;
     }
     if (n > NOALLOC_MAX_N) {
@@ -146,25 +149,12 @@ extern "C" int booth_sm100_reduce_f32_noalloc(sm100_ptr_t in, long long n, sm100
                      n, NOALLOC_MAX_N, NOALLOC_SLOTS, NOALLOC_SEGMENT);
         return SM100_ERR_ARG;
     }
-    int device = -1;
-    cudaError_t e = cudaGetDevice(&device);
-    if (e != cudaSuccess) return fail("cudaGetDevice", e);
-    if (device < 0 || device >= NOALLOC_MAX_DEVICES) {
-        std::fprintf(stderr, "sm100_rt: booth_sm100_reduce_f32_noalloc: device ordinal %d not supported\n", device);
-        return SM100_ERR_ARG;
-    }
-    unsigned char *scratch;
-    {
-        // Once per device, with that device current: the device address of the array.
-        std::lock_guard<std::mutex> lock(g_setup_mutex);
-        if (!g_scratch_addr[device]) {
-            void *p = nullptr;
-            e = cudaGetSymbolAddress(&p, g_scratch);
-            if (e != cudaSuccess) return fail("cudaGetSymbolAddress(scratch)", e);
-            g_scratch_addr[device] = static_cast<unsigned char *>(p);
-        }
-        scratch = g_scratch_addr[device];
-    }
+    // The device address of the array on the current device. In host code the name
+    // g_scratch is not that address; only this call yields one a kernel can use.
+    void *sym = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&sym, g_scratch);
+    if (e != cudaSuccess) return fail("cudaGetSymbolAddress(scratch)", e);
+    unsigned char *scratch = static_cast<unsigned char *>(sym);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     // The array keeps the previous call's contents; only the counter must be zero.
     e = cudaMemsetAsync(scratch, 0, NOALLOC_HEADER, s);

@@ -73,7 +73,7 @@ enum {
     SM100_K_REDUCE_I32, SM100_K_REDUCE_F32,
     SM100_K_ASIAN_MC, SM100_K_ASIAN_MC_PRECISE,
     SM100_K_ASIAN_PATHS, SM100_K_ASIAN_PATHS_PRECISE,
-    SM100_K_GEMM_SPLIT_A, SM100_K_GEMM_SPLIT_BT, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_ZERO_TILES,
+    SM100_K_GEMM_PREPASS, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128,
     SM100_K_COUNT
 };
 
@@ -105,6 +105,10 @@ struct sm100_dev {
     int         stage_ready;
     int         gemm_pending;          /* a GEMM was enqueued since the last status check */
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
+    unsigned    gemm_wait_ms;          /* limit of the GEMM kernel's barrier waits */
+    /* The GEMM's four tensor maps (64-byte aligned, allocated on first use) and what they were encoded for. */
+    CUtensorMap *gemm_maps;
+    struct { CUdeviceptr ws; int Mp, Np, Kp, box_b, valid; } gemm_maps_key;
     /* Which B the split planes in the workspace belong to (booth_sm100_gemm_ex reuses them on request). */
     struct { CUdeviceptr b, planes; int K, N, valid; } gemm_b;
     /* Snapshot of the most recent dispatch (kernel, geometry, first bytes of the
@@ -131,12 +135,18 @@ int  sm100_launch_k3(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsi
  * finishing (programmatic stream serialization). */
 int  sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
                                unsigned shmem, void **args);
+int  sm100_launch_k3_overlapped(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsigned gz,
+                                unsigned bx, unsigned by, unsigned bz, unsigned shmem, void **args);
 /* The kernel's name as the driver knows it, for messages; "kernel" when the driver
  * cannot say (cuFuncGetName is a CUDA 12.3 entry point). */
 void sm100_func_name(sm100_dev_t *dev, void *func, char *out, size_t n);
 /* Grows the device-owned scratch / GEMM workspace; returns 0 on failure. */
 CUdeviceptr sm100_scratch(sm100_dev_t *dev, size_t bytes);
 CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes);
+
+/* Reads the status word of a GEMM enqueued since the last check (the stream must
+ * be idle): SM100_OK, or SM100_ERR_CUDA with the text recorded and printed. */
+int  sm100_gemm_outcome(sm100_dev_t *dev);
 
 /* The embedded sm_100a kernel image (image.S). */
 extern const unsigned char booth_sm100_image[];

@@ -147,7 +147,7 @@ static const char *const k_names[SM100_K_COUNT] = {
     "reduce_sum_i32", "reduce_sum_f32",
     "asian_mc", "asian_mc_precise",
     "asian_paths", "asian_paths_precise",
-    "gemm_split_a", "gemm_split_bt", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta", "gemm_tf32x3_2cta_n128", "gemm_zero_tiles",
+    "gemm_prepass", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta", "gemm_tf32x3_2cta_n128",
 };
 
 int sm100_rt_device_count(void)
@@ -231,6 +231,11 @@ int sm100_rt_init(sm100_dev_t **out, int ordinal)
         (cr = a->StreamSynchronize(d->stream)) != CUDA_SUCCESS) {
         rc = sm100_fail(NULL, "clearing scratch", cr); a->MemFree(d->scratch); goto drop_image;
     }
+    {   /* limit of the GEMM kernel's barrier waits: BOOTH_SM100_GEMM_WAIT_MS at start-up, else 4 s */
+        const char *e = getenv("BOOTH_SM100_GEMM_WAIT_MS");
+        int ms = (e && *e) ? atoi(e) : 4000;
+        d->gemm_wait_ms = (unsigned)(ms < 1 ? 1 : ms > 60000 ? 60000 : ms);
+    }
     fprintf(stderr, "sm100_rt: device %d: %s (sm_%d%d, %d SMs)\n", ordinal, d->name,
             d->sm_major, d->sm_minor, d->sm_count);
     *out = d;
@@ -268,6 +273,7 @@ void sm100_rt_shut(sm100_dev_t *dev)
         a->StreamDestroy(dev->stream);
     }
     a->PrimaryCtxRelease(dev->cudev);
+    free(dev->gemm_maps);
     free(dev);
 }
 
@@ -414,6 +420,29 @@ void sm100_rt_unload(sm100_dev_t *dev, sm100_kern_t *kern)
     memset(kern, 0, sizeof *kern);
 }
 
+/* ---- outcome of an enqueued GEMM ---- */
+
+/* The GEMM kernel bounds its barrier waits and reports an expired one in a status
+ * word instead of hanging. Every entry point that has just waited for the stream
+ * (sync, the synchronous copies, toc, free) calls this, so a caller that goes from
+ * booth_sm100_gemm straight to a copy back learns of it too. The stream must be
+ * idle when this is called. */
+int sm100_gemm_outcome(sm100_dev_t *dev)
+{
+    if (!dev->gemm_pending) return SM100_OK;
+    int st = 0;
+    dev->gemm_pending = 0;
+    CUresult cr = dev->api->MemcpyDtoH(&st, dev->scratch + SM100_SCRATCH_GEMM_STATUS, sizeof st);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "reading GEMM status", cr);
+    if (st != 0) {
+        snprintf(dev->err, sizeof dev->err, "gemm_tf32x3 gave up waiting on a barrier (code %d: "
+                 "1 = producer, 2 = MMA issuer on operands, 3 = epilogue, 4 = MMA issuer on a free accumulator)", st);
+        fprintf(stderr, "sm100_rt: %s\n", dev->err);
+        return SM100_ERR_CUDA;
+    }
+    return SM100_OK;
+}
+
 /* ---- memory ---- */
 
 sm100_ptr_t sm100_rt_alloc(sm100_dev_t *dev, size_t size)
@@ -433,7 +462,11 @@ sm100_ptr_t sm100_rt_alloc(sm100_dev_t *dev, size_t size)
 void sm100_rt_free(sm100_dev_t *dev, sm100_ptr_t ptr)
 {
     if (!ptr || sm100_enter(dev) != SM100_OK) return;
-    dev->api->StreamSynchronize(dev->stream);
+    /* cuMemFree itself waits for the work that may still use the block. Only a
+     * GEMM whose outcome nobody has asked for yet needs a wait of our own: its
+     * status is read (and a failure printed) before the memory goes away. */
+    if (dev->gemm_pending && dev->api->StreamSynchronize(dev->stream) == CUDA_SUCCESS)
+        (void)sm100_gemm_outcome(dev);
     dev->api->MemFree((CUdeviceptr)ptr);
 }
 
@@ -448,7 +481,8 @@ int sm100_rt_h2d(sm100_dev_t *dev, sm100_ptr_t dst, const void *src, size_t size
      * for: a kernel launched right after could read stale data. */
     CUresult cr = dev->api->MemcpyHtoDAsync((CUdeviceptr)dst, src, size, dev->stream);
     if (cr == CUDA_SUCCESS) cr = dev->api->StreamSynchronize(dev->stream);
-    return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "h2d copy", cr);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "h2d copy", cr);
+    return sm100_gemm_outcome(dev);
 }
 
 int sm100_rt_d2h(sm100_dev_t *dev, void *dst, sm100_ptr_t src, size_t size)
@@ -458,7 +492,8 @@ int sm100_rt_d2h(sm100_dev_t *dev, void *dst, sm100_ptr_t src, size_t size)
     if (size == 0) return SM100_OK;
     CUresult cr = dev->api->MemcpyDtoHAsync(dst, (CUdeviceptr)src, size, dev->stream);
     if (cr == CUDA_SUCCESS) cr = dev->api->StreamSynchronize(dev->stream);
-    return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "d2h copy", cr);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "d2h copy", cr);
+    return sm100_gemm_outcome(dev);
 }
 
 int sm100_rt_h2d_async(sm100_dev_t *dev, sm100_ptr_t dst, const void *src, size_t size)
@@ -653,23 +688,23 @@ int sm100_launch_k(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
     return sm100_launch_k3(dev, which, grid, 1, 1, block, 1, 1, shmem, args);
 }
 
-int sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
-                              unsigned shmem, void **args)
+int sm100_launch_k3_overlapped(sm100_dev_t *dev, int which, unsigned gx, unsigned gy, unsigned gz,
+                               unsigned bx, unsigned by, unsigned bz, unsigned shmem, void **args)
 {
     static int enabled = -1;
     if (enabled < 0) {
         const char *e = getenv("BOOTH_SM100_PDL");
         enabled = !(e && e[0] == '0');
     }
-    if (!enabled || !dev->api->LaunchKernelEx) return sm100_launch_k(dev, which, grid, block, shmem, args);
+    if (!enabled || !dev->api->LaunchKernelEx) return sm100_launch_k3(dev, which, gx, gy, gz, bx, by, bz, shmem, args);
     CUlaunchAttribute attr;
     memset(&attr, 0, sizeof attr);
     attr.id = CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION;
     attr.value.programmaticStreamSerializationAllowed = 1;
     CUlaunchConfig cfg;
     memset(&cfg, 0, sizeof cfg);
-    cfg.gridDimX = grid; cfg.gridDimY = 1; cfg.gridDimZ = 1;
-    cfg.blockDimX = block; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.gridDimX = gx; cfg.gridDimY = gy; cfg.gridDimZ = gz;
+    cfg.blockDimX = bx; cfg.blockDimY = by; cfg.blockDimZ = bz;
     cfg.sharedMemBytes = shmem;
     cfg.hStream = dev->stream;
     cfg.attrs = &attr;
@@ -677,11 +712,18 @@ int sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsign
     CUresult cr = dev->api->LaunchKernelEx(&cfg, dev->k[which], args, NULL);
     if (cr != CUDA_SUCCESS) {
         char what[160];
-        snprintf(what, sizeof what, "cuLaunchKernelEx '%s' grid %u block %u shmem %u", k_names[which], grid, block, shmem);
+        snprintf(what, sizeof what, "cuLaunchKernelEx '%s' grid %ux%ux%u block %ux%ux%u shmem %u", k_names[which],
+                 gx, gy, gz, bx, by, bz, shmem);
         return sm100_fail(dev, what, cr);
     }
     dev->launches++;
     return SM100_OK;
+}
+
+int sm100_launch_k_overlapped(sm100_dev_t *dev, int which, unsigned grid, unsigned block,
+                              unsigned shmem, void **args)
+{
+    return sm100_launch_k3_overlapped(dev, which, grid, 1, 1, block, 1, 1, shmem, args);
 }
 
 int sm100_rt_sync(sm100_dev_t *dev)
@@ -690,21 +732,7 @@ int sm100_rt_sync(sm100_dev_t *dev)
     if (rc != SM100_OK) return rc;
     CUresult cr = dev->api->StreamSynchronize(dev->stream);
     if (cr != CUDA_SUCCESS) { rc = sm100_fail(dev, "sync", cr); dump_trak(dev); return rc; }
-    if (dev->gemm_pending) {
-        /* The GEMM kernel bounds its barrier waits and reports an expired one
-         * in a status word instead of hanging. */
-        int st = 0;
-        dev->gemm_pending = 0;
-        cr = dev->api->MemcpyDtoH(&st, dev->scratch + SM100_SCRATCH_GEMM_STATUS, sizeof st);
-        if (cr != CUDA_SUCCESS) return sm100_fail(dev, "reading GEMM status", cr);
-        if (st != 0) {
-            snprintf(dev->err, sizeof dev->err, "gemm_tf32x3 gave up waiting on a barrier (code %d: "
-                     "1 = producer, 2 = MMA issuer on operands, 3 = epilogue, 4 = MMA issuer on a free accumulator)", st);
-            fprintf(stderr, "sm100_rt: %s\n", dev->err);
-            return SM100_ERR_CUDA;
-        }
-    }
-    return SM100_OK;
+    return sm100_gemm_outcome(dev);
 }
 
 int sm100_rt_tic(sm100_dev_t *dev)
@@ -722,5 +750,6 @@ int sm100_rt_toc(sm100_dev_t *dev, float *ms)
     CUresult cr = dev->api->EventRecord(dev->ev1, dev->stream);
     if (cr == CUDA_SUCCESS) cr = dev->api->EventSynchronize(dev->ev1);
     if (cr == CUDA_SUCCESS && ms) cr = dev->api->EventElapsedTime(ms, dev->ev0, dev->ev1);
-    return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "event timing", cr);
+    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "event timing", cr);
+    return sm100_gemm_outcome(dev);
 }

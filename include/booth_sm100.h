@@ -142,16 +142,26 @@ unsigned long long sm100_rt_launches(const sm100_dev_t *dev);
  *   kind 0: float  uniform in [-1,1):   2*u - 1,  u = (x >> 8) * 2^-24
  *   kind 1: float  uniform in [0,1):    u
  *   kind 2: int32  uniform in [-1000,1000]:  (int)(x % 2001) - 1000
+ *   kind 3: uint32 the generator's output word x itself
  * The device and host generators give identical bits. first is the index of
  * the first element written to dst (dst[0] is element `first`), so a shard can
  * be generated in place. */
 #define BOOTH_FILL_F32_PM1   0
 #define BOOTH_FILL_F32_01    1
 #define BOOTH_FILL_I32_1000  2
+#define BOOTH_FILL_U32_RAW   3
 int  booth_sm100_fill(sm100_dev_t *dev, sm100_ptr_t dst, long long first,
                       long long n, uint32_t seed, uint32_t stream, int kind);
 void booth_sm100_fill_host(void *dst, long long first, long long n,
                            uint32_t seed, uint32_t stream, int kind, int threads);
+/* One Philox4x32-10 block on the host (Salmon et al., SC'11; the generator behind
+ * the seeded inputs and the Monte Carlo pricer): counter ctr[0..3], key key[0..1].
+ * The image also carries a kernel "philox_words(out, c0, c1, c2, c3, k0, k1)"
+ * (sm100_rt_load_builtin) whose thread t writes the block of counter
+ * (c0 + t, c1, c2, c3) to out[4t..4t+3]. Both exist so the generator can be held
+ * against the known-answer vectors published with Random123; no counterpart in
+ * the reference, whose pricer uses a counter hash (src/ocaml/Asian.ml:8-30). */
+void booth_sm100_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
 
 /* out[i] = x[i] + y[i]: tests/tri_vadd.py:6-16, tests/vector_add.cu:4-10. */
 int  booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y,
@@ -171,7 +181,9 @@ int  booth_sm100_vadd_host(sm100_dev_t *dev, const float *x, const float *y, flo
 int  booth_sm100_saxpy_host(sm100_dev_t *dev, float *y, const float *x, float a, long long n);
 /* Sum of n int32 with wrapping arithmetic into *out (one int32 on the device):
  * the tg_reduce / reduce_sum shape, tests/tg_reduce.cu:4-26,
- * tests/canonical.cu:59-108. */
+ * tests/canonical.cu:59-108. For both sums in must be 4-byte aligned and out
+ * aligned to the result's size (4 bytes here, 8 for the fp32 sum's double);
+ * anything else returns SM100_ERR_ARG before any GPU work. */
 int  booth_sm100_reduce_i32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
                             sm100_ptr_t out);
 /* Sum of n float into out[0] (double) on the device; fp32 per-thread partial
@@ -184,10 +196,11 @@ int  booth_sm100_reduce_f32(sm100_dev_t *dev, sm100_ptr_t in, long long n,
  * runtime's current device and on `stream` (a cudaStream_t, NULL for the default
  * stream) and keeps its segment sums in a 33,024-byte array built into the
  * library, so n is limited to 2^30 elements; larger n returns SM100_ERR_ARG.
- * out[0] (double, device memory) receives the sum. The first call on a device
- * resolves the array's address and loads the library's device code there: make
- * it before any stream capture. Calls share the array: do not let two of them
- * overlap on the GPU. This entry point has no counterpart in the reference. */
+ * out[0] (double, device memory, 8-byte aligned) receives the sum; in must be
+ * 4-byte aligned; both are checked before any GPU work. The first call on a device
+ * loads the library's device code there: make it before any stream capture. Calls
+ * share the array: do not let two of them overlap on the GPU. This entry point has
+ * no counterpart in the reference. */
 int  booth_sm100_reduce_f32_noalloc(sm100_ptr_t in, long long n, sm100_ptr_t out, void *stream);
 /* C[M,N] = A[M,K] * B[K,N], row-major fp32, 3xTF32 on the tensor cores:
  * the tests/tri_matmul_k.py:8-23 / tests/canonical.cu:18-50 contraction. Any
@@ -203,8 +216,20 @@ int  booth_sm100_gemm(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a,
  * replicated B, the reference's sharding of this workload. No counterpart in the
  * reference. */
 #define BOOTH_GEMM_B_UNCHANGED 1u
+/* Test hook, never set it in production: the kernel's TMA producers issue nothing,
+ * so its bounded barrier waits run out and the failure report can be observed
+ * without faulting the device (the call leaves C unwritten and the next wait on
+ * the stream returns SM100_ERR_CUDA). */
+#define BOOTH_GEMM_TEST_SILENT_PRODUCER 0x80000000u
 int  booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a,
                          sm100_ptr_t b, int M, int N, int K, unsigned flags);
+/* How long a barrier wait inside the GEMM kernel may last before the kernel gives
+ * up, records which wait it was and returns (1..60000 ms; 4000 unless the
+ * environment variable BOOTH_SM100_GEMM_WAIT_MS said otherwise at sm100_rt_init).
+ * The outcome of a GEMM is reported by the next call that waits for the stream:
+ * sm100_rt_sync, sm100_rt_d2h, sm100_rt_h2d, sm100_rt_toc (sm100_rt_free prints
+ * it). */
+int  booth_sm100_gemm_wait_limit(sm100_dev_t *dev, unsigned ms);
 
 /* Asian-option Monte Carlo (src/ocaml/Asian.ml:32-72 with Philox4x32-10 in
  * place of its counter hash). drift = (r - sigma^2/2)*dt and vol = sigma*sqrt(dt)
@@ -215,8 +240,8 @@ typedef struct booth_asian {
     uint32_t k0, k1;            /* Philox key */
     int32_t  precise;           /* 0: MUFU approximations, 1: libm-accurate functions */
 } booth_asian_t;
-/* Prices paths [path0, path0+npaths) and writes four doubles to out on the
- * device: sum of arithmetic payoffs, sum of geometric payoffs, and the sums of
+/* Prices paths [path0, path0+npaths) and writes four doubles to out (8-byte
+ * aligned) on the device: sum of arithmetic payoffs, sum of geometric payoffs, and the sums of
  * their squares (undiscounted). */
 int  booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
                        long long npaths, sm100_ptr_t out);
@@ -256,8 +281,9 @@ void sm100_comm_destroy(sm100_comm_t *comm);
 
 /* ---------------------------------------------------------------------------
  * CPU-launcher symbols (host pointers; stage to the GPU, launch, copy back)
- * The signatures are those of examples/cpu_launch_vadd.c:23-24 and
- * examples/cpu_launch_matmul.c:22-26: the kernel's own parameters followed by
+ * The signatures are those of examples/cpu_launch_vadd.c:23-24 (also
+ * tests/diff/diff_vadd.c:28-29) and examples/cpu_launch_matmul.c:22-26: the
+ * kernel's own parameters followed by
  * nthreads (src/cpu/cpu_emit.c:386-431). They have no error channel; on failure
  * they print "sm100_rt: ..." and abort(), they never compute on the CPU.
  * ------------------------------------------------------------------------- */
@@ -270,6 +296,9 @@ void matmul_k(float *a, float *b, float *c, int K, int stride_am, int stride_ak,
               int stride_bk, int stride_bn, int stride_cm, int stride_cn,
               int nthreads);
 void saxpy(float *y, float *x, float a, int n, int nthreads);
+/* The guarded vector add of tests/ocaml/vadd_k.bir as tests/build/run_vadd.c:12
+ * declares it: c[i] = a[i] + b[i] for i < min(n, nthreads). */
+void vadd(const float *a, const float *b, float *c, int n, int nthreads);
 
 #ifdef __cplusplus
 }

@@ -35,6 +35,10 @@ extern void asian_paths(float *arith, float *geom, long long path0,
                         unsigned int k0, unsigned int k1, float s0, float strike,
                         float drift, float vol, int nstep, long long nthreads);
 
+extern void philox_words(unsigned int *out, unsigned int c0, unsigned int c1,
+                         unsigned int c2, unsigned int c3, unsigned int k0,
+                         unsigned int k1, long long nthreads);
+
 /* ---- a small static-schedule parallel-for ---- */
 
 typedef void (*orc_body_fn)(void *ctx, long long lo, long long hi);
@@ -276,4 +280,69 @@ void orc_asian(long long path0, long long npaths, unsigned k0, unsigned k1,
     for (long long b = 0; b < nb; b++) { sa += m.bsum[2 * b]; sg += m.bsum[2 * b + 1]; }
     free(m.bsum);
     sums[0] = sa; sums[1] = sg;
+}
+
+/* ---- Philox4x32-10: the kernel object's words, and the seeded input stream ---- */
+
+/* nblocks output blocks of the philox_words kernel (the reference compiler's
+ * object in libbooth_ref, the restatement in libbooth_port): counter
+ * (ctr[0] + t, ctr[1], ctr[2], ctr[3]), key (key[0], key[1]). */
+void orc_philox_kernel(const unsigned *ctr, const unsigned *key, long long nblocks, unsigned *out)
+{
+    philox_words(out, ctr[0], ctr[1], ctr[2], ctr[3], key[0], key[1], nblocks);
+}
+
+/* The harness's own statement of the generator, used by orc_fill below to make
+ * benchmark inputs without touching the product library. */
+static void orc_philox_block(uint32_t c[4], uint32_t k0, uint32_t k1)
+{
+    for (int r = 0; r < 10; r++) {
+        uint64_t p0 = (uint64_t)0xD2511F53u * c[0];
+        uint64_t p1 = (uint64_t)0xCD9E8D57u * c[2];
+        uint32_t n0 = (uint32_t)(p1 >> 32) ^ c[1] ^ k0;
+        uint32_t n2 = (uint32_t)(p0 >> 32) ^ c[3] ^ k1;
+        c[0] = n0; c[1] = (uint32_t)p1; c[2] = n2; c[3] = (uint32_t)p0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+}
+
+void orc_philox_host(const unsigned *ctr, const unsigned *key, unsigned *out)
+{
+    uint32_t c[4] = { ctr[0], ctr[1], ctr[2], ctr[3] };
+    orc_philox_block(c, key[0], key[1]);
+    for (int i = 0; i < 4; i++) out[i] = c[i];
+}
+
+/* The workloads' seeded input stream: element i is lane i%4 of the block with
+ * counter (i/4 low word, i/4 high word, 0, 0) and key (seed, stream).
+ *   kind 0: float in [-1,1)  2u-1, u = (x >> 8) * 2^-24      kind 1: float u in [0,1)
+ *   kind 2: int32 in [-1000,1000]  (int)(x % 2001) - 1000    kind 3: the raw word x
+ * dst[0] is element `first`. */
+typedef struct { uint32_t *dst; long long first; uint32_t seed, stream; int kind; } fill_ctx;
+static void fill_body(void *cx, long long lo, long long hi)
+{
+    fill_ctx *f = (fill_ctx *)cx;
+    long long i = lo;
+    while (i < hi) {
+        long long e = f->first + i;
+        unsigned long long ctr = (unsigned long long)e >> 2;
+        uint32_t c[4] = { (uint32_t)ctr, (uint32_t)(ctr >> 32), 0, 0 };
+        orc_philox_block(c, f->seed, f->stream);
+        for (int l = (int)(e & 3); l < 4 && i < hi; l++, i++) {
+            uint32_t x = c[l], v = x;
+            if (f->kind == 2) {
+                v = (uint32_t)((int)(x % 2001u) - 1000);
+            } else if (f->kind != 3) {
+                float u = (float)(x >> 8) * 5.9604644775390625e-8f;
+                float g = f->kind == 0 ? 2.0f * u - 1.0f : u;
+                memcpy(&v, &g, 4);
+            }
+            f->dst[i] = v;
+        }
+    }
+}
+void orc_fill(void *dst, long long first, long long n, unsigned seed, unsigned stream, int kind, int threads)
+{
+    fill_ctx c = { (uint32_t *)dst, first, seed, stream, kind };
+    orc_parallel(fill_body, &c, n, 4096, threads);
 }

@@ -132,6 +132,17 @@ static void philox4x32_10(uint32_t c[4], uint32_t k0, uint32_t k1)
     }
 }
 
+/* ---- raw Philox words: oracle/kernels/philox_words.cu ---- */
+void philox_words(unsigned int *out, unsigned int c0, unsigned int c1, unsigned int c2,
+                  unsigned int c3, unsigned int k0, unsigned int k1, long long nthreads)
+{
+    for (long long t = 0; t < nthreads; t++) {
+        uint32_t c[4] = { c0 + (uint32_t)t, c1, c2, c3 };
+        philox4x32_10(c, k0, k1);
+        for (int i = 0; i < 4; i++) out[4 * t + i] = c[i];
+    }
+}
+
 void asian_paths(float *arith, float *geom, long long path0, unsigned int k0,
                  unsigned int k1, float s0, float strike, float drift, float vol,
                  int nstep, long long nthreads)

@@ -9,6 +9,9 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
+# The reference tree, when present: BOOTH_REF, else a checkout named "reference"
+# beside this repository. Tests that need it skip their reference half without it.
+REFERENCE = os.environ.get("BOOTH_REF") or os.path.join(os.path.dirname(ROOT), "reference")
 
 
 def pytest_configure(config):
@@ -42,14 +45,26 @@ def dev(sm):
     d.close()
 
 
-def philox_np(ctr, seed, stream):
-    """Philox4x32-10 in numpy: counter (ctr low, ctr high, 0, 0), key (seed, stream).
+# Known-answer vectors of Philox4x32-10 as published with the Random123 library
+# (Salmon, Moraes, Dror, Shaw, SC'11; its kat_vectors file): (counter, key, output).
+PHILOX_KAT = (
+    ((0x00000000, 0x00000000, 0x00000000, 0x00000000), (0x00000000, 0x00000000),
+     (0x6627e8d5, 0xe169c58d, 0xbc57ac4c, 0x9b00dbd8)),
+    ((0xffffffff, 0xffffffff, 0xffffffff, 0xffffffff), (0xffffffff, 0xffffffff),
+     (0x408f276d, 0x41c83b0e, 0xa20bc7c6, 0x6d5451fd)),
+    ((0x243f6a88, 0x85a308d3, 0x13198a2e, 0x03707344), (0xa4093822, 0x299f31d0),
+     (0xd16cfe09, 0x94fdcceb, 0x5001e420, 0x24126ea1)),
+)
+
+
+def philox_np(ctr, seed, stream, c2=0, c3=0):
+    """Philox4x32-10 in numpy: counter (ctr low, ctr high, c2, c3), key (seed, stream).
     Independent restatement used to pin the C and CUDA generators."""
     ctr = np.asarray(ctr, dtype=np.uint64)
     c0 = (ctr & np.uint64(0xFFFFFFFF)).astype(np.uint64)
     c1 = (ctr >> np.uint64(32)).astype(np.uint64)
-    c2 = np.zeros_like(c0)
-    c3 = np.zeros_like(c0)
+    c2 = np.zeros_like(c0) + np.uint64(c2)
+    c3 = np.zeros_like(c0) + np.uint64(c3)
     k0, k1 = np.uint64(seed), np.uint64(stream)
     M0, M1, MASK = np.uint64(0xD2511F53), np.uint64(0xCD9E8D57), np.uint64(0xFFFFFFFF)
     for _ in range(10):
@@ -70,5 +85,7 @@ def fill_np(first, n, seed, stream, kind):
     x = words[np.arange(n), (idx & np.uint64(3)).astype(np.int64)]
     if kind == 2:
         return (x % np.uint32(2001)).astype(np.int32) - np.int32(1000)
+    if kind == 3:
+        return x
     u = (x >> np.uint32(8)).astype(np.float32) * np.float32(2.0 ** -24)
     return (np.float32(2) * u - np.float32(1)) if kind == 0 else u

@@ -10,6 +10,9 @@
  * so that a test can check which kernels the host code launches, in which order
  * and with which geometry, without a GPU. FAKE_CUDA_FAIL=<entry point>:<k> makes
  * the k-th call of that entry point return an error (host-side fault injection).
+ * FAKE_CUDA_GEMM_STATUS=<code> makes a launch of a gemm_tf32x3* kernel store that
+ * code in the kernel's status word (its eleventh parameter), the way the real
+ * kernel does when one of its bounded waits runs out.
  * The device it reports is an sm_100 part with 148 SMs.
  */
 #define _POSIX_C_SOURCE 200809L
@@ -157,6 +160,13 @@ CUresult cuEventRecord(CUevent e, CUstream s) { (void)e; (void)s; return CUDA_SU
 CUresult cuEventSynchronize(CUevent e) { (void)e; return CUDA_SUCCESS; }
 CUresult cuEventElapsedTime(float *ms, CUevent a, CUevent b) { (void)a; (void)b; *ms = 1.0f; return CUDA_SUCCESS; }
 
+static void gemm_status(CUfunction f, void **params)
+{
+    const char *code = getenv("FAKE_CUDA_GEMM_STATUS");
+    if (code && params && strncmp(((fake_func_t *)f)->name, "gemm_tf32x3", 11) == 0)
+        *(int *)(size_t)*(CUdeviceptr *)params[10] = atoi(code);
+}
+
 static CUresult record_launch(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                               unsigned shmem, int overlap, void **extra)
 {
@@ -177,13 +187,14 @@ static CUresult record_launch(CUfunction f, unsigned gx, unsigned gy, unsigned g
 CUresult cuLaunchKernel(CUfunction f, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                         unsigned shmem, CUstream s, void **params, void **extra)
 {
-    (void)s; (void)params;
+    (void)s;
+    gemm_status(f, params);
     return record_launch(f, gx, gy, gz, bx, by, bz, shmem, 0, extra);
 }
 CUresult cuLaunchKernelEx(const CUlaunchConfig *c, CUfunction f, void **params, void **extra)
 {
     int overlap = 0;
-    (void)params;
+    gemm_status(f, params);
     for (unsigned i = 0; i < c->numAttrs; i++)
         if (c->attrs[i].id == CU_LAUNCH_ATTRIBUTE_PROGRAMMATIC_STREAM_SERIALIZATION)
             overlap = c->attrs[i].value.programmaticStreamSerializationAllowed;

@@ -9,7 +9,7 @@ import sys
 
 import numpy as np
 
-from conftest import ROOT, fill_np
+from conftest import REFERENCE, ROOT, fill_np
 
 
 def _declared(header):
@@ -149,7 +149,7 @@ def test_run_side_descriptor_mirrors_the_reference_contract(sm, tmp_path):
     dev_size, kern_size = words[2] & 0xFFFFFFFF, words[2] >> 32
     assert 0 < dev_size <= 1024 and 0 < kern_size <= 192   # RT_DEV_MAX / RT_KERN_MAX (src/exec/exec.h:43-44)
     assert all(words[i] != 0 for i in range(3, 17))        # 10 required + 4 optional operations
-    ref_hdr = "/root/reference/src/exec/exec.h"
+    ref_hdr = os.path.join(REFERENCE, "src", "exec", "exec.h")
     if not os.path.exists(ref_hdr):
         return
     probe = r"""

@@ -126,7 +126,7 @@ def test_gemm_full_size_sampled_rows(sm, dev, oracle_lib, size):
 @pytest.mark.parametrize("pair", ["1", "0"])
 def test_barrier_wait_limit_reports_instead_of_hanging(sm, pair):
     """Failure detection without a fault: with the TMA producer kept silent (a
-    host-side switch) nothing ever signals the "operands ready" barrier, so the MMA
+    host-side flag of the call) nothing ever signals the "operands ready" barrier, so the MMA
     issuer's and the epilogue's bounded waits run out (limit 50 ms here), the
     kernel records which wait gave up, frees its tensor memory and returns; the
     host reads the status at the next sync. The device stays usable."""
@@ -136,13 +136,13 @@ d = sm.Device(0)
 M = N = 512; K = 256
 a = sm.fill_host(M * K, 5, 0, 0); b = sm.fill_host(K * N, 5, 1, 0)
 da, db, dc = d.upload(a), d.upload(b), d.alloc(M * N * 4)
-os.environ["BOOTH_SM100_GEMM_WAIT_MS"] = "50"; os.environ["BOOTH_SM100_GEMM_SILENT_PRODUCER"] = "1"
-d.gemm(dc, da, db, M, N, K)
+d.gemm_wait_limit(50)
+d.gemm(dc, da, db, M, N, K, flags=sm.GEMM_TEST_SILENT_PRODUCER)
 try:
-    d.sync(); print("no error reported")
+    d.download(dc, 4, np.float32); print("no error reported")       # any call that waits reports it
 except sm.Sm100Error as e:
     print("reported:", e)
-os.environ["BOOTH_SM100_GEMM_SILENT_PRODUCER"] = "0"; os.environ["BOOTH_SM100_GEMM_WAIT_MS"] = "4000"
+d.gemm_wait_limit(4000)
 d.gemm(dc, da, db, M, N, K); d.sync()
 c = d.download(dc, (M, N), np.float32).astype(np.float64)
 ref = a.reshape(M, K).astype(np.float64) @ b.reshape(K, N).astype(np.float64)

@@ -83,21 +83,105 @@ d.sync(); d.close()
                        ("reduce_sum_f32", (1, 1, 1), 256), ("asian_mc", (4736, 1, 1), 256),
                        ("asian_mc_precise", (4, 1, 1), 256)]
     g = seq[5:]
-    # 4096^3: split A (one 16-byte chunk per thread), split B (64 x 64 tiles), zero the 34 shared tiles,
-    # then 256 + 34 clusters of two CTAs with 197,632 bytes of dynamic shared memory
-    assert g[:4] == [("gemm_split_a", (16384, 1, 1), 256), ("gemm_split_bt", (64, 64, 1), 256),
-                     ("gemm_zero_tiles", (34, 1, 1), 256), ("gemm_tf32x3_2cta", (580, 1, 1), 320)]
-    assert L[5 + 3]["shmem"] == 197632
-    # same B declared unchanged: no B split
-    assert [k for k, _, _ in g[4:7]] == ["gemm_split_a", "gemm_zero_tiles", "gemm_tf32x3_2cta"]
+    # 4096^3: ONE launch ahead of the contraction (16384 blocks split A, one 16-byte chunk per thread;
+    # 64 x 64 blocks split and transpose B; 34 blocks zero the shared tiles), then 256 + 34 clusters of two
+    # CTAs with 197,632 bytes of dynamic shared memory; both launched with programmatic stream serialization
+    assert g[:2] == [("gemm_prepass", (16384 + 4096 + 34, 1, 1), 256), ("gemm_tf32x3_2cta", (580, 1, 1), 320)]
+    assert L[5 + 1]["shmem"] == 197632 and L[5]["overlap"] == 1 and L[5 + 1]["overlap"] == 1
+    # same B declared unchanged: no B blocks
+    assert g[2:4] == [("gemm_prepass", (16384 + 34, 1, 1), 256), ("gemm_tf32x3_2cta", (580, 1, 1), 320)]
     # 8192^3 (1024 tiles = 13 waves + 62: too many leftovers to share): B split again despite the flag
-    assert g[7:10] == [("gemm_split_a", (65536, 1, 1), 256), ("gemm_split_bt", (128, 128, 1), 256),
-                       ("gemm_tf32x3_2cta", (2048, 1, 1), 320)]
+    assert g[4:6] == [("gemm_prepass", (65536 + 16384, 1, 1), 256), ("gemm_tf32x3_2cta", (2048, 1, 1), 320)]
     # 100 x 200 x 50 pads to 128 x 256 x 64: the one-CTA form, one tile
-    assert g[10:] == [("gemm_split_a", (8, 1, 1), 256), ("gemm_split_bt", (4, 1, 1), 256),
-                      ("gemm_tf32x3", (1, 1, 1), 320)]
+    assert g[6:] == [("gemm_prepass", (8 + 4, 1, 1), 256), ("gemm_tf32x3", (1, 1, 1), 320)]
     maps = [ln for ln in lines if ln.startswith("tensormap")]
     assert maps[-4:] == ["tensormap dims 64 128 stride 256 box 32 128"] * 2 + ["tensormap dims 64 256 stride 256 box 32 256"] * 2
+    # the maps are encoded once per (workspace, padded shape): the two 4096^3 calls share theirs
+    assert len(maps) == 3 * 4
+
+
+def test_gemm_outcome_reaches_every_call_that_waits(fake, tmp_path):
+    """A GEMM whose bounded wait ran out leaves a code in its status word. The caller
+    learns of it from whichever call waits for the stream next, not only from
+    sm100_rt_sync: here the fake sets the word at the launch and the copy back
+    (what Device.download, bc_copy_d2h and nv_rt_d2h do after a GEMM) reports it."""
+    res, L, _ = run(fake, tmp_path, """
+import numpy as np
+d = sm.Device(0); x = d.alloc(1 << 20); y = d.alloc(1 << 20); out = d.alloc(1 << 20)
+for waiter in ("download", "toc", "sync", "h2d"):
+    d.tic()
+    d.gemm(out, x, y, 256, 256, 64)
+    try:
+        if waiter == "download": d.download(out, 4, np.float32)
+        elif waiter == "toc": d.toc()
+        elif waiter == "h2d": d.h2d(x, np.zeros(4, np.float32))
+        else: d.sync()
+        print(waiter, "no error")
+    except sm.Sm100Error as e:
+        print(waiter, "reported", e.code, "code 3" in str(e))
+    d.sync()                                   # reported once; the device is usable again
+d.close()
+""", FAKE_CUDA_GEMM_STATUS="3")
+    assert res.returncode == 0, res.stderr
+    for waiter in ("download", "toc", "sync", "h2d"):
+        assert "%s reported -3 True" % waiter in res.stdout
+    assert res.stderr.count("gave up waiting on a barrier (code 3") == 4
+
+
+def test_bad_result_addresses_are_refused_before_any_launch(fake, tmp_path):
+    """A misaligned result address would fault on the device; the host refuses it."""
+    res, L, _ = run(fake, tmp_path, """
+d = sm.Device(0); x = d.alloc(4096); out = d.alloc(64)
+def rc(f, *a):
+    try: f(*a); return 0
+    except sm.Sm100Error as e: return e.code
+print("f32 out+4", rc(d.reduce_f32, x, 100, out + 4), "i32 out+4", rc(d.reduce_i32, x, 100, out + 4),
+      "i32 out+2", rc(d.reduce_i32, x, 100, out + 2), "null in", rc(d.reduce_f32, 0, 100, out),
+      "null in n=0", rc(d.reduce_f32, 0, 0, out), "in+2", rc(d.reduce_i32, x + 2, 100, out),
+      "asian out+4", rc(d.asian, sm.asian_params(), 0, 1000, out + 4))
+print("noalloc out+4", sm.lib().booth_sm100_reduce_f32_noalloc(x, 100, out + 4, None),
+      "noalloc null in", sm.lib().booth_sm100_reduce_f32_noalloc(0, 100, out, None))
+d.close()
+""")
+    assert res.returncode == 0, res.stderr
+    assert "f32 out+4 -7 i32 out+4 0 i32 out+2 -7 null in -7 null in n=0 0 in+2 -7 asian out+4 -7" in res.stdout
+    assert "noalloc out+4 -7 noalloc null in -7" in res.stdout
+    assert [l["kernel"] for l in L] == ["reduce_sum_i32", "reduce_sum_f32"]     # only the two valid calls launched
+
+
+def test_reference_booth_run_drives_the_registered_descriptor(fake, tmp_path):
+    """The reference's own command line (src/exec/booth_run.c, with src/exec/execs.c's
+    registration list holding &rt_sm100) over the fake driver: target lookup,
+    rt_open, rt_load, staging, one launch with the geometry of the command line,
+    the copy back and the written file; and its answers for an unknown target and an
+    unknown kernel. Results are not looked at here (nothing computes)."""
+    exe = os.path.join(ROOT, "build", "examples", "booth-run")
+    if not os.path.exists(exe):
+        pytest.skip("build/examples/booth-run was not built (the reference tree was absent at build time)")
+    import numpy as np
+    cubin = os.path.join(ROOT, "booth_b200", "lib", "booth_sm100.cubin")
+    np.arange(1024, dtype=np.float32).tofile(tmp_path / "x.bin")
+    np.ones(1024, np.float32).tofile(tmp_path / "y.bin")
+    log = tmp_path / "driver.log"
+    env = dict(os.environ, BOOTH_CUDA_LIB=fake, FAKE_CUDA_LOG=str(log))
+    for target in (["--target", "sm100"], []):              # by name, and by probing the list
+        log.write_text("")
+        res = subprocess.run([exe, cubin, "saxpy"] + target + ["--grid", "4", "--block", "256", "io:" + str(tmp_path / "y.bin"),
+                              "in:" + str(tmp_path / "x.bin"), "f32:2.5", "u32:1024"], env=env, stdout=subprocess.PIPE,
+                             stderr=subprocess.PIPE, text=True, timeout=60)
+        assert res.returncode == 0, res.stderr
+        assert "wrote %s (4096 bytes)" % (tmp_path / "y.bin") in res.stdout
+        ops = [" ".join(ln.split()[:2]) for ln in log.read_text().splitlines()]
+        assert ops == ["h2d 4096", "h2d 4096", "launch saxpy", "d2h 4096"]
+        assert "launch saxpy grid 4 1 1 block 256 1 1 shmem 0" in log.read_text()
+    res = subprocess.run([exe, cubin, "saxpy", "--target", "nvptx"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert res.returncode == 2 and "no target named 'nvptx'. Known: sm100" in res.stderr
+    res = subprocess.run([exe, cubin, "no_such_kernel", "--target", "sm100"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert res.returncode == 1 and "no kernel of that name in the cubin" in res.stderr
+    # too many argument bytes for the kernel's parameter block: refused by the descriptor's run
+    res = subprocess.run([exe, cubin, "saxpy", "--target", "sm100", "io:" + str(tmp_path / "y.bin"), "in:" + str(tmp_path / "x.bin"),
+                          "f32:2.5", "u32:1024", "u32:7", "u32:8"], env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert res.returncode == 1 and "launch:" in res.stderr
 
 
 def test_bc_dispatch_cuts_oversized_argument_blocks_and_is_synchronous(fake, tmp_path):
@@ -385,3 +469,8 @@ def test_nothing_is_computed_on_the_host(fake, tmp_path):
     res = subprocess.run([os.path.join(ex, "cpu_launch_vadd")], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                          text=True, timeout=60)
     assert "MISMATCH" in res.stdout and "OK" not in res.stdout.replace("MISMATCH", "")
+    # the reference's differential harness and its BIR-kernel check fail the same way
+    res = subprocess.run([os.path.join(ex, "diff_vadd")], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=60)
+    assert res.returncode != 0 and "FAIL" in res.stdout
+    res = subprocess.run([os.path.join(ex, "run_vadd")], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, timeout=60)
+    assert res.returncode != 0 and "MISMATCH" in res.stdout

@@ -10,11 +10,11 @@ import subprocess
 import numpy as np
 import pytest
 
-from conftest import ROOT
+from conftest import ROOT, REFERENCE
 
 EXAMPLES = os.path.join(ROOT, "build", "examples")
 PTX = os.path.join(ROOT, "oracle", "_ref", "ptx")
-REF_HDR = "/root/reference/src/nvidia/nv_rt.h"
+REF_HDR = os.path.join(REFERENCE, "src", "nvidia", "nv_rt.h")
 NAMES = ["nv_rt_init", "nv_rt_shut", "nv_rt_load", "nv_rt_unload", "nv_rt_alloc", "nv_rt_free",
          "nv_rt_h2d", "nv_rt_d2h", "nv_rt_launch", "nv_rt_sync", "nv_rt_mmap", "nv_rt_mfre"]
 
