@@ -37,9 +37,31 @@ LOG2_PATHS = 26             # Monte Carlo paths per GPU
 NSTEP = 252
 GEMM_SIZES = (4096, 8192)
 BYTES_PER_ELEM = {"saxpy": 12, "vadd": 12, "reduce": 4}
-# DRAM bytes per element per launch as counted by ncu (dram__bytes_read.sum +
-# dram__bytes_write.sum); see the summaries under profiles/. None = not captured.
-NCU_TRAFFIC_PER_ELEM = {"saxpy": 11.67, "vadd": 11.77, "reduce_i32": 4.03, "reduce_f32": 4.03}
+CHECK_PIECE = 1 << 26       # elements the CPU checker generates and sums at a time
+CHECK_WINDOW = 1 << 20      # elements per saxpy window / Monte Carlo paths per rank checked
+TOL = {"fp32_sum": 1e-6, "mc": 1e-5, "gemm": 1e-5}     # the workloads' stated tolerances
+
+
+def ncu_traffic():
+    """DRAM bytes per unit per launch as counted by ncu (dram__bytes_read.sum +
+    dram__bytes_write.sum): the one table profiles/dram_traffic_per_unit.md holds,
+    keyed by its first column. A key that is not there has not been captured."""
+    table = {}
+    try:
+        with open(os.path.join(ROOT, "profiles", "dram_traffic_per_unit.md")) as f:
+            for ln in f:
+                cells = [c.strip() for c in ln.strip().strip("|").split("|")]
+                if len(cells) >= 4 and ln.lstrip().startswith("|"):
+                    try:
+                        table[cells[0]] = float(cells[3])
+                    except ValueError:
+                        pass
+    except OSError:
+        pass
+    return table
+
+
+NCU_TRAFFIC = ncu_traffic()
 
 
 def measured_peaks():
@@ -153,6 +175,23 @@ class Ranks:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t[0])
 
+    def sum(self, values, integer=False):
+        """Element-wise sum over ranks of a short list (float64, or int64 when integer)."""
+        if not self.dist:
+            return list(values)
+        import torch
+        t = torch.tensor(list(values), dtype=torch.int64 if integer else torch.float64)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.SUM)
+        return [int(v) if integer else float(v) for v in t]
+
+    def gather(self, v):
+        """One float per rank, on every rank."""
+        if not self.dist:
+            return [float(v)]
+        box = [None] * self.world
+        self.dist.all_gather_object(box, float(v))
+        return box
+
     def bcast_bytes(self, b):
         if not self.dist:
             return b
@@ -190,23 +229,57 @@ def timed_short(dev, ranks, warmup, steps, body, repeats=3):
     return runs[len(runs) // 2]
 
 
-def mufu_ceiling(path_steps_per_s, sm_count, clocks):
-    """The pricer is bound by the special-function unit, not by HBM or the tensor
-    pipe: 3 MUFU operations per path-step on 16 MUFU lanes per SM allow at most
-    16/3 path-steps per clock per SM. Reported per GPU at the SM clock sampled
-    during the timed region."""
+def mc_rooflines(path_steps_per_s, sm_count, clocks):
+    """The pricer is bound by neither HBM nor the tensor pipe. Two issue limits
+    apply per SM and clock: the special-function unit (3 MUFU operations per
+    path-step on 16 lanes: 16/3 path-steps) and the warp schedulers (20.8 warp
+    instructions per warp-step as counted by ncu, 4 schedulers x 32 lanes:
+    128/20.8 path-steps). Reported per GPU at the SM clock sampled during the
+    timed region; the lower of the two ceilings is the `roofline`."""
     mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz")
+    clock_source = "sampled during the timed region"
     if not mhz:
-        return None
+        mhz, clock_source = 1965.0, "no clock sample available: the B200's maximum SM clock assumed"
     achieved = path_steps_per_s / (sm_count * mhz * 1e6)
-    return {"bound": "mufu issue", "achieved": achieved, "peak": 16.0 / 3.0, "unit": "path-steps/clk/SM",
-            "frac": achieved / (16.0 / 3.0), "sm_mhz": mhz}
+    mufu = {"bound": "mufu issue", "achieved": achieved, "peak": 16.0 / 3.0, "unit": "path-steps/clk/SM",
+            "frac": achieved / (16.0 / 3.0), "traffic": None, "sm_mhz": mhz, "sm_mhz_source": clock_source,
+            "peak_source": "derived: 16 MUFU lanes per SM / 3 MUFU operations per path-step"}
+    issue = {"bound": "warp instruction issue", "achieved": achieved, "peak": 128.0 / 20.8, "unit": "path-steps/clk/SM",
+             "frac": achieved / (128.0 / 20.8),
+             "peak_source": "derived: 4 schedulers x 32 lanes / 20.8 warp instructions per warp-step (ncu, profiles/asian_mc_2p22.md)"}
+    return mufu, issue
 
 
 def roofline(bound, achieved, peak, unit, traffic, peaks):
-    return {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
-            "frac": achieved / peak if peak else None, "traffic": traffic,
-            "peak_source": "of " + peaks["source"]}
+    r = {"bound": bound, "achieved": achieved, "peak": peak, "unit": unit,
+         "frac": achieved / peak if peak else None, "traffic": traffic,
+         "peak_source": "of " + peaks["source"]}
+    if bound == "hbm":
+        r["frac_of_nominal_8TBs"] = achieved / 8000.0
+    if peak and achieved > peak:
+        r["warning"] = ("above the denominator: the measured peak is a plain copy (half reads, half writes) / a cuBLAS "
+                        "bf16 GEMM scaled to 3xTF32, neither is a hard ceiling for this kernel; read the nominal "
+                        "fraction beside it")
+    return r
+
+
+def wall(ranks, steps, body):
+    """End-to-end timing of a host-buffer call: one untimed call, then `steps`
+    calls on the wall clock between barriers (each call returns with its result in
+    host memory); max over ranks, seconds, plus every rank's own time."""
+    body()
+    ranks.barrier()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        body()
+    mine = time.perf_counter() - t0
+    ranks.barrier()
+    return ranks.max(mine), ranks.gather(mine)
+
+
+def wrap32(v):
+    v &= 0xFFFFFFFF
+    return v - (1 << 32) if v & 0x80000000 else v
 
 
 def run_ours(args):
@@ -222,6 +295,19 @@ def run_ours(args):
     G = ranks.world
     workloads = []
     sampler = ClockSampler(ranks.local)
+    # The CPU checker: used outside every timed region to check results (all ranks)
+    # and, on rank 0 of a 1-GPU run, as the timed CPU baseline. Never the product path.
+    orc = None
+    if not args.no_parity or (ranks.rank == 0 and G == 1 and not args.no_cpu_baseline):
+        import oracle
+        orc = oracle.load()
+    parity, misses = {}, []
+    Ke = max(1, min(K, args.e2e_steps))
+
+    def check(name, ok, detail):
+        parity[name] = detail
+        if not ok:
+            misses.append(name)
 
     n = 1 << args.log2n
     first = ranks.rank * n                      # this rank's contiguous shard of the global vectors
@@ -239,12 +325,28 @@ def run_ours(args):
     saxpy_ms = ms / K
     saxpy_gbs = BYTES_PER_ELEM["saxpy"] * n * G / (saxpy_ms * 1e-3) / 1e9
     per_gpu = saxpy_gbs / G
-    t_el = NCU_TRAFFIC_PER_ELEM["saxpy"]
+    t_el = NCU_TRAFFIC.get("saxpy")
     head_roof = roofline("hbm", per_gpu, peaks["hbm_gbs"], "GB/s", t_el * n if t_el else None, peaks)
-    head_roof["frac_of_nominal_8TBs"] = per_gpu / 8000.0
 
-    # ---- e2e: the launcher API with host buffers (the examples/launch_saxpy.c flow) ----
-    e2e = None if args.no_e2e else run_e2e_saxpy(sm, dev, ranks, n, max(1, min(K, args.e2e_steps)))
+    if not args.no_parity:
+        # saxpy parity at the benchmark's own size and shard: fresh inputs, one launch over
+        # all n elements, three windows of this rank's shard against the CPU checker on the
+        # same elements of the global stream, bit for bit.
+        dev.fill(dy, first, n, SEED + 1, 1, sm.FILL_F32_PM1)
+        dev.saxpy(dy, dx, 2.5, n)
+        wlen = min(CHECK_WINDOW, n)
+        bad = 0
+        for off in sorted({0, (n // 2 - wlen // 2 + 5) if n > wlen else 0, n - wlen}):
+            hx = orc.fill(wlen, SEED + 1, 0, sm.FILL_F32_PM1, first=first + off)
+            hy = orc.fill(wlen, SEED + 1, 1, sm.FILL_F32_PM1, first=first + off)
+            got = dev.download(dy + 4 * off, wlen, np.float32)
+            bad += int(np.count_nonzero(got.view(np.uint32) != orc.saxpy(hy, hx, 2.5).view(np.uint32)))
+        bad = int(ranks.sum([bad], integer=True)[0])
+        check("saxpy_mismatches", bad == 0, bad)
+        dev.fill(dy, first, n, SEED + 1, 1, sm.FILL_F32_PM1)
+
+    # ---- e2e: host buffers in, result back in host memory, through the library's calls ----
+    e2e = None if args.no_e2e else run_e2e_saxpy(sm, dev, ranks, n, Ke)
     want = set(args.workloads.split(",")) if args.workloads != "all" else {"sweep", "vadd", "reduce", "asian", "gemm"}
     if args.headline_only:
         want = set()
@@ -264,19 +366,33 @@ def run_ours(args):
             dz = dev.alloc(m * 4)
             t = (timed_short if lg < 28 else timed)(dev, ranks, W, K, lambda: dev.vadd(dx, dy, dz, m)) / K
             gbs = 12.0 * m / (t * 1e-3) / 1e9
+            t_el = NCU_TRAFFIC.get("vadd")
             workloads.append({"name": "vadd_2^%d" % lg, "metric": "hbm_gbs", "value": gbs * G, "unit": "GB/s",
                               "ms_per_step": t,
                               "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s",
-                                                   NCU_TRAFFIC_PER_ELEM["vadd"] * m if lg > 26 else None, peaks),
+                                                   t_el * m if (t_el and lg > 26) else None, peaks),
                               "note": "201 MB working set, partly L2-resident; median of 3 runs of K steps" if lg == LOG2_VADD else "3 GiB working set"})
             dev.free(dz)
+            if not args.no_e2e:
+                # end to end: the host-vector call behind the CPU-launcher symbol vector_add
+                hv = [dev.hostalloc(m * 4) for _ in range(3)]
+                for i in (0, 1):
+                    sm.lib().booth_sm100_fill_host(hv[i], first, m, SEED + 1, i, sm.FILL_F32_PM1, 16)
+                dt_s, per_rank = wall(ranks, Ke, lambda: dev.vadd_host(hv[0], hv[1], hv[2], m))
+                workloads[-1]["e2e"] = {"value": 12.0 * m * G * Ke / dt_s / 1e9, "unit": "GB/s", "steps": Ke,
+                                        "h2d_bytes_per_step": 8 * m * G, "d2h_bytes_per_step": 4 * m * G,
+                                        "per_rank_s": per_rank, "api": "booth_sm100_vadd_host on pinned host vectors"}
+                for hp in hv:
+                    dev.hostfree(hp)
 
     out = dev.alloc(64)
     if "reduce" in want:
         # ---- reduction (config 2): per-GPU sum then one NCCL all-reduce ----
+        hostv = None if args.no_e2e else dev.hostalloc(n * 4)
         for name, kind, fn, dt in (("reduce_i32", sm.FILL_I32_1000, dev.reduce_i32, sm.I32),
                                    ("reduce_f32", sm.FILL_F32_01, dev.reduce_f32, sm.F64)):
-            dev.fill(dx, first, n, SEED + 2, 0 if dt == sm.I32 else 1, kind)
+            stream_id = 0 if dt == sm.I32 else 1
+            dev.fill(dx, first, n, SEED + 2, stream_id, kind)
 
             def step():
                 fn(dx, n, out)
@@ -285,10 +401,45 @@ def run_ours(args):
             t = timed(dev, ranks, W, K, step) / K
             res = dev.download(out, 1, np.int32 if dt == sm.I32 else np.float64)[0]
             gbs = 4.0 * n / (t * 1e-3) / 1e9
-            workloads.append({"name": name + "_2^%d" % args.log2n, "metric": "hbm_gbs", "value": gbs * G, "unit": "GB/s",
-                              "ms_per_step": t, "result": float(res), "allreduce": bool(comm),
-                              "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s",
-                                                   NCU_TRAFFIC_PER_ELEM[name] * n, peaks)})
+            entry = {"name": name + "_2^%d" % args.log2n, "metric": "hbm_gbs", "value": gbs * G, "unit": "GB/s",
+                     "ms_per_step": t, "result": float(res), "allreduce": bool(comm),
+                     "roofline": roofline("hbm", gbs, peaks["hbm_gbs"], "GB/s",
+                                          NCU_TRAFFIC[name] * n if name in NCU_TRAFFIC else None, peaks)}
+            if not args.no_parity:
+                # the all-reduced sum against the CPU checker's sum of the same global stream:
+                # every rank sums its own shard on the host cores, generated piece by piece,
+                # and the partial sums are added over the process group
+                acc_i, acc_f = 0, 0.0
+                for off in range(0, n, CHECK_PIECE):
+                    m = min(CHECK_PIECE, n - off)
+                    piece = orc.fill(m, SEED + 2, stream_id, kind, first=first + off)
+                    if dt == sm.I32:
+                        acc_i = wrap32(acc_i + orc.reduce_i32(piece))
+                    else:
+                        acc_f += orc.reduce_f32(piece)
+                if dt == sm.I32:
+                    ref = wrap32(int(ranks.sum([acc_i], integer=True)[0]))
+                    check("int32", int(res) == ref, "bit-exact" if int(res) == ref else "device %d != checker %d" % (int(res), ref))
+                else:
+                    ref = ranks.sum([acc_f])[0]
+                    rel = abs(float(res) - ref) / abs(ref)
+                    check("fp32_rel", rel <= TOL["fp32_sum"], rel)
+            if hostv:
+                # end to end: the vector starts in page-locked host memory, one scalar comes back
+                sm.lib().booth_sm100_fill_host(hostv, first, n, SEED + 2, stream_id, kind, 16)
+
+                def host_step():
+                    dev.h2d_async(dx, hostv, n * 4)
+                    step()
+                    dev.download(out, 1, np.int32 if dt == sm.I32 else np.float64)
+                dt_s, per_rank = wall(ranks, Ke, host_step)
+                entry["e2e"] = {"value": 4.0 * n * G * Ke / dt_s / 1e9, "unit": "GB/s", "steps": Ke,
+                                "h2d_bytes_per_step": 4 * n * G, "d2h_bytes_per_step": (4 if dt == sm.I32 else 8) * G,
+                                "api": "sm100_rt_h2d_async + booth_sm100_%s%s + sm100_rt_d2h" % (name, " + sm100_comm_allreduce_sum" if comm else ""),
+                                "per_rank_s": per_rank}
+            workloads.append(entry)
+        if hostv:
+            dev.hostfree(hostv)
 
     if "asian" in want:
         # ---- Asian-option Monte Carlo (config 4): disjoint Philox subsequences per GPU ----
@@ -308,18 +459,41 @@ def run_ours(args):
             s = dev.download(out, 4, np.float64)
             tot = npaths * G
             disc = math.exp(-0.05)
-            workloads.append({"name": "asian_mc_%s_2^%d_paths_per_gpu" % ("precise" if precise else "fast", args.log2paths),
-                              "metric": "paths_per_s", "value": tot / (t * 1e-3), "unit": "paths/s",
-                              "path_steps_per_s": tot * NSTEP / (t * 1e-3), "ms_per_step": t,
-                              "price_arith": disc * s[0] / tot, "price_geom": disc * s[1] / tot,
-                              "stderr_geom": disc * math.sqrt(max(s[3] / tot - (s[1] / tot) ** 2, 0.0) / tot),
-                              "allreduce": bool(comm), "clocks": mc_clocks,
-                              "mufu_ceiling": mufu_ceiling(npaths * NSTEP / (t * 1e-3), dev.sm_count, mc_clocks)})
+            mufu, issue = mc_rooflines(npaths * NSTEP / (t * 1e-3), dev.sm_count, mc_clocks)
+            entry = {"name": "asian_mc_%s_2^%d_paths_per_gpu" % ("precise" if precise else "fast", args.log2paths),
+                     "metric": "paths_per_s", "value": tot / (t * 1e-3), "unit": "paths/s",
+                     "path_steps_per_s": tot * NSTEP / (t * 1e-3), "ms_per_step": t,
+                     "price_arith": disc * s[0] / tot, "price_geom": disc * s[1] / tot,
+                     "stderr_geom": disc * math.sqrt(max(s[3] / tot - (s[1] / tot) ** 2, 0.0) / tot),
+                     "allreduce": bool(comm), "clocks": mc_clocks, "roofline": mufu, "second_bound": issue}
+            if not args.no_e2e:
+                # end to end: parameters in (a 32-byte struct by value), four doubles back
+                def mc_host_step():
+                    mc_step()
+                    dev.download(out, 4, np.float64)
+                dt_s, per_rank = wall(ranks, max(1, min(Ke, ksteps)), mc_host_step)
+                ke = max(1, min(Ke, ksteps))
+                entry["e2e"] = {"value": tot * ke / dt_s, "unit": "paths/s", "steps": ke, "h2d_bytes_per_step": 32 * G,
+                                "d2h_bytes_per_step": 32 * G, "per_rank_s": per_rank,
+                                "api": "booth_sm100_asian%s + sm100_rt_d2h" % (" + sm100_comm_allreduce_sum" if comm else "")}
+            if not args.no_parity:
+                # a check-sized run of the same kernel on this rank's own subsequence, all-reduced,
+                # against the CPU checker over the union of the ranks' ranges
+                cp = min(CHECK_WINDOW, npaths)
+                dev.asian(prm, ranks.rank * cp, cp, out)
+                if comm:
+                    comm.allreduce_sum(out, 4, sm.F64)
+                got = dev.download(out, 4, np.float64)
+                ref = ranks.sum(list(orc.asian(prm, ranks.rank * cp, cp)))
+                rels = [abs(got[i] - ref[i]) / abs(ref[i]) for i in range(2)]
+                check("mc_rel_%s" % ("precise" if precise else "fast"), max(rels) <= TOL["mc"], rels)
+            workloads.append(entry)
 
     if "gemm" in want:
         # ---- fp32 GEMM (config 3): row blocks of A per GPU, B replicated ----
         sizes = [int(v) for v in args.gemm_sizes.split(",")]
-        workloads.extend(run_gemm(sm, dev, ranks, peaks, W, K, sizes))
+        workloads.extend(run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc if not args.no_parity else None, check,
+                                  0 if args.no_e2e else Ke))
 
     line = {
         "metric": "saxpy_hbm_gbs", "value": saxpy_gbs, "unit": "GB/s", "n_gpus": G, "steps": K, "warmup": W,
@@ -333,13 +507,15 @@ def run_ours(args):
                              "inputs (%.3g MiB per GPU) fit the 126 MB L2: not an HBM figure" % (8.0 * n / 2 ** 20))},
         "e2e": e2e, "gpu_launches": int(launches), "clocks": clocks,
         "roofline": head_roof,
+        "parity": dict(parity, checker=orc.kind, tolerances=TOL, checked_on="all %d rank(s), outside the timed regions" % G,
+                       status="green" if not misses else "MISS: " + ", ".join(misses)) if not args.no_parity else None,
         "workloads": workloads,
         "device": dev.name,
     }
     if ranks.rank == 0 and G == 1 and not args.no_cpu_baseline:
-        line["cpu_baseline"] = cpu_baseline_saxpy(args.cpu_seconds)
+        line["cpu_baseline"] = cpu_baseline_saxpy(orc, args.cpu_seconds)
         if workloads:
-            others = cpu_baselines_other()
+            others = cpu_baselines_other(orc)
             for wl in workloads:
                 for fam, base in others.items():
                     if wl["name"].startswith(fam if fam != "asian" else "asian_mc") and "value" in wl:
@@ -351,11 +527,17 @@ def run_ours(args):
     if ranks.rank == 0:
         emit(line)
     ranks.close()
+    if misses:
+        sys.stderr.write("bench: PARITY MISS on %s\n" % ", ".join(misses))
+        raise SystemExit(3)
 
 
 def run_e2e_saxpy(sm, dev, ranks, n, steps):
-    """The bc_* launcher API end to end: pinned host x and y go to the device,
-    the saxpy kernel is dispatched by name, y comes back. Every byte counted."""
+    """The headline workload end to end: pinned host x and y go to the device, y
+    comes back, every byte counted. Two forms: the pipelined host-vector call
+    (booth_sm100_saxpy_host, the figure), and the synchronous bc_* flow of the
+    reference's example program beside it. The link itself is measured in the same
+    run so the figure reads as a fraction of something measured."""
     import ctypes as C
     L = sm.lib()
     os.environ["BOOTH_DEVICE"] = str(ranks.local)
@@ -382,14 +564,7 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps):
         if L.bc_dispatch(C.byref(bcd), C.byref(k), blocks, 1, 1, 256, 1, 1, C.byref(a), C.sizeof(a)) != 0:
             raise RuntimeError("bc_dispatch failed")
         L.bc_copy_d2h(C.byref(bcd), hy, dy, nbytes)
-    step()
-    ranks.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        step()
-    dt = time.perf_counter() - t0
-    ranks.barrier()
-    dt = ranks.max(dt)
+    dt, _ = wall(ranks, steps, step)
     L.bc_free(C.byref(bcd), dx); L.bc_free(C.byref(bcd), dy)
     L.bc_unload_kernel(C.byref(bcd), C.byref(k))
     L.bc_device_shutdown(C.byref(bcd))
@@ -397,23 +572,37 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps):
                 "api": "bc_copy_h2d x2 + bc_dispatch(saxpy) + bc_copy_d2h (the examples/launch_saxpy.c flow), synchronous"}
 
     # The pipelined host-vector call: same pinned buffers, same bytes, both link directions busy at once.
-    dev.saxpy_host(hy, hx, 2.5, n)
-    ranks.barrier()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        dev.saxpy_host(hy, hx, 2.5, n)
-    dt = ranks.max(time.perf_counter() - t0)
-    ranks.barrier()
+    dt, per_rank = wall(ranks, steps, lambda: dev.saxpy_host(hy, hx, 2.5, n))
     dev.hostfree(hx); dev.hostfree(hy)
-    return {"value": 12.0 * n * ranks.world * steps / dt / 1e9, "unit": "GB/s", "steps": steps,
+    value = 12.0 * n * ranks.world * steps / dt / 1e9
+    # The link, measured alone on this rank while the others do the same (so at N > 1 the
+    # ranks share the host's memory and root complexes as they do in the timed calls).
+    ranks.barrier()
+    up, down, up2, down2 = dev.link_probe(min(1 << 30, max(nbytes, 1 << 16)), 3)
+    ranks.barrier()
+    # 2 bytes go up for every byte that comes down; with both directions busy the call
+    # cannot end before the slower of (8n / up-rate) and (4n / down-rate).
+    bound_s = max(2.0 * nbytes / (up2 * 1e9), 1.0 * nbytes / (down2 * 1e9)) if up2 > 0 and down2 > 0 else None
+    peak = 12.0 * n / bound_s / 1e9 if bound_s else None
+    mine = 12.0 * n * steps / per_rank[ranks.rank] / 1e9
+    fracs = ranks.gather(mine / peak if peak else 0.0)
+    return {"value": value, "unit": "GB/s", "steps": steps,
             "h2d_bytes_per_step": 2 * nbytes * ranks.world, "d2h_bytes_per_step": nbytes * ranks.world,
             "bytes_scope": "whole job (all GPUs), like value",
             "api": "booth_sm100_saxpy_host on pinned host vectors: 16 Mi-element chunks, H2D / saxpy / D2H pipelined "
-                   "on two streams; returns with y in host memory",
+                   "on three streams; returns with y in host memory",
+            "roofline": {"bound": "pcie", "unit": "GB/s", "achieved": mine, "peak": peak,
+                         "frac": mine / peak if peak else None,
+                         "peak_source": "measured in this run on rank 0's GPU (booth_sm100_link_probe, 3 x 1 GiB pinned copies): "
+                                        "H2D %.1f, D2H %.1f alone; %.1f and %.1f with both directions busy; peak = 12 B x N / "
+                                        "max(8N/up, 4N/down)" % (up, down, up2, down2),
+                         "link_gbs": {"h2d": up, "d2h": down, "h2d_duplex": up2, "d2h_duplex": down2},
+                         "frac_per_rank": fracs},
+            "per_rank_s": per_rank,
             "launcher_api": launcher}
 
 
-def run_gemm(sm, dev, ranks, peaks, W, K, sizes):
+def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps):
     out = []
     G = ranks.world
     # 3xTF32: three TF32 MMAs per fp32 product; TF32 dense rate is half the bf16 rate.
@@ -435,26 +624,65 @@ def run_gemm(sm, dev, ranks, peaks, W, K, sizes):
         # call: the split, transposed copy of B in the workspace is reused. Reported
         # beside the full figure, never in its place.
         t_kept = timed(dev, ranks, W, K, lambda: dev.gemm(c, a, b, M, size, size, b_unchanged=True)) / K
-        out.append({"name": "gemm_fp32_3xtf32_%d" % size, "metric": "tflops", "value": tf, "unit": "TFLOP/s",
-                    "ms_per_step": t, "sharding": "A/C row blocks of %d rows per GPU, B replicated" % M,
-                    "b_unchanged": {"value": 2.0 * size * size * size / (t_kept * 1e-3) / 1e12, "unit": "TFLOP/s",
-                                    "ms_per_step": t_kept,
-                                    "note": "booth_sm100_gemm_ex(BOOTH_GEMM_B_UNCHANGED): B's planes kept from the previous call"},
-                    "roofline": dict(roofline("tensor", tf / G, peak, "TFLOP/s", None, peaks),
-                                     frac_of_sustained_peak=tf / G / (peaks["bf16_tflops_sustained"] / 6.0)),
-                    "hbm_bytes": 4.0 * (M * size + size * size + M * size)})
+        traffic = NCU_TRAFFIC.get("gemm_%d" % size) if G == 1 else None
+        entry = {"name": "gemm_fp32_3xtf32_%d" % size, "metric": "tflops", "value": tf, "unit": "TFLOP/s",
+                 "ms_per_step": t, "sharding": "A/C row blocks of %d rows per GPU, B replicated" % M,
+                 "b_unchanged": {"value": 2.0 * size * size * size / (t_kept * 1e-3) / 1e12, "unit": "TFLOP/s",
+                                 "ms_per_step": t_kept,
+                                 "note": "booth_sm100_gemm_ex(BOOTH_GEMM_B_UNCHANGED): B's planes kept from the previous call"},
+                 "roofline": dict(roofline("tensor", tf / G, peak, "TFLOP/s", traffic, peaks),
+                                  frac_of_sustained_peak=tf / G / (peaks["bf16_tflops_sustained"] / 6.0),
+                                  traffic_note="DRAM bytes of the contraction kernel per launch (ncu); above the algorithmic "
+                                               "hbm_bytes because it reads the split planes (2x) and re-reads panels: "
+                                               "harmless, the kernel is bound by the tensor pipe" if traffic else
+                                               "not captured for this shape"),
+                 "hbm_bytes": 4.0 * (M * size + size * size + M * size)}
+        if orc is not None:
+            # 16 four-row blocks of this rank's rows of C against the CPU checker's 4x4x2 tiles
+            # on the same seeded inputs (only the sampled rows of A are generated on the host)
+            dev.gemm(c, a, b, M, size, size)
+            dev.sync()
+            rng = np.random.default_rng(size * 131 + ranks.rank)
+            nblk = min(16, M // 4)
+            rows4 = np.sort(rng.choice(M // 4, size=nblk, replace=False))
+            hb = orc.fill(size * size, SEED + 3, 1, sm.FILL_F32_PM1).reshape(size, size)
+            ha = np.concatenate([orc.fill(4 * size, SEED + 3, 0, sm.FILL_F32_PM1,
+                                          first=(ranks.rank * M + 4 * int(r)) * size) for r in rows4]).reshape(4 * nblk, size)
+            want = orc.matmul(ha, hb).astype(np.float64)
+            got = np.concatenate([dev.download(c + 4 * int(r) * size * 4, (4, size), np.float32) for r in rows4]).astype(np.float64)
+            num2, den2 = ranks.sum([float(((got - want) ** 2).sum()), float((want ** 2).sum())])
+            rel = math.sqrt(num2 / den2)
+            check("gemm_rel_fro_%d" % size, rel <= 1e-5, rel)
+            del hb, ha
+        if e2e_steps:
+            # end to end: A's row block and B in page-locked host memory, C back to the host
+            na, nb = M * size * 4, size * size * 4
+            ha_p, hb_p, hc_p = dev.hostalloc(na), dev.hostalloc(nb), dev.hostalloc(na)
+            sm.lib().booth_sm100_fill_host(ha_p, ranks.rank * M * size, M * size, SEED + 3, 0, sm.FILL_F32_PM1, 16)
+            sm.lib().booth_sm100_fill_host(hb_p, 0, size * size, SEED + 3, 1, sm.FILL_F32_PM1, 16)
+
+            def host_step():
+                dev.h2d_async(a, ha_p, na)
+                dev.h2d_async(b, hb_p, nb)
+                dev.gemm(c, a, b, M, size, size)
+                dev.d2h_async(hc_p, c, na)
+                dev.sync()
+            dt_s, per_rank = wall(ranks, e2e_steps, host_step)
+            entry["e2e"] = {"value": 2.0 * size ** 3 * e2e_steps / dt_s / 1e12, "unit": "TFLOP/s", "steps": e2e_steps,
+                            "h2d_bytes_per_step": (na + nb) * G, "d2h_bytes_per_step": na * G, "per_rank_s": per_rank,
+                            "api": "sm100_rt_h2d_async(A, B) + booth_sm100_gemm + sm100_rt_d2h_async(C) + sm100_rt_sync"}
+            for hp in (ha_p, hb_p, hc_p):
+                dev.hostfree(hp)
+        out.append(entry)
         for p in (a, b, c):
             dev.free(p)
     return out
 
 
-def cpu_baselines_other(seconds_each=3.0):
+def cpu_baselines_other(orc, seconds_each=3.0):
     """The CPU checker timed on bounded samples of the other four workloads, all
     host threads over disjoint ranges (the reference compiler's x86-64 objects when
     they are built here). Returned keyed by workload family."""
-    import oracle
-    import booth_b200 as sm
-    orc = oracle.load()
     out = {}
 
     def run(fn, units, unit, sample):
@@ -470,32 +698,44 @@ def cpu_baselines_other(seconds_each=3.0):
                 "sample": "%s x %d repetitions, %d threads" % (sample, reps, orc.cores)}
 
     m = 1 << 26
-    x = sm.fill_host(m, SEED, 0, sm.FILL_F32_PM1, threads=orc.cores)
-    y = sm.fill_host(m, SEED, 1, sm.FILL_F32_PM1, threads=orc.cores)
+    x = orc.fill(m, SEED, 0, 0)
+    y = orc.fill(m, SEED, 1, 0)
     out["vadd"] = run(lambda: orc.vadd(x, y), 12.0 * m / 1e9, "GB/s", "vector add on 2^26 elements")
-    vi = sm.fill_host(m, SEED + 2, 0, sm.FILL_I32_1000, threads=orc.cores)
+    vi = orc.fill(m, SEED + 2, 0, 2)
     out["reduce_i32"] = run(lambda: orc.reduce_i32(vi), 4.0 * m / 1e9, "GB/s", "int32 sum of 2^26 elements")
-    vf = sm.fill_host(m, SEED + 2, 1, sm.FILL_F32_01, threads=orc.cores)
+    vf = orc.fill(m, SEED + 2, 1, 1)
     out["reduce_f32"] = run(lambda: orc.reduce_f32(vf), 4.0 * m / 1e9, "GB/s", "fp32 sum of 2^26 elements")
     g = 1024
-    a = sm.fill_host(g * g, SEED + 3, 0, sm.FILL_F32_PM1).reshape(g, g)
-    b = sm.fill_host(g * g, SEED + 3, 1, sm.FILL_F32_PM1).reshape(g, g)
+    a = orc.fill(g * g, SEED + 3, 0, 0).reshape(g, g)
+    b = orc.fill(g * g, SEED + 3, 1, 0).reshape(g, g)
     out["gemm"] = run(lambda: orc.matmul(a, b), 2.0 * g ** 3 / 1e12, "TFLOP/s", "1024^3 GEMM by 4x4x2 tiles")
-    prm = sm.asian_params(k0=SEED + 5)
+    prm = asian_params_host()
     npth = 1 << 20
     out["asian"] = run(lambda: orc.asian(prm, 0, npth), float(npth), "paths/s", "2^20 paths x 252 steps")
     return out
 
 
-def cpu_baseline_saxpy(seconds):
+class _AsianParams:
+    pass
+
+
+def asian_params_host(k0=SEED + 5):
+    """The pricer's parameters for the CPU checker, computed in fp32 as the workload
+    states them (drift = (r - sigma^2/2) dt, vol = sigma sqrt(dt)); no product code."""
+    p = _AsianParams()
+    dt = np.float32(1.0) / np.float32(NSTEP)
+    p.s0, p.strike, p.nstep, p.k0, p.k1 = 100.0, 100.0, NSTEP, k0, 0
+    p.drift = float((np.float32(0.05) - np.float32(0.5) * np.float32(0.2) * np.float32(0.2)) * dt)
+    p.vol = float(np.float32(0.2) * np.sqrt(dt, dtype=np.float32))
+    return p
+
+
+def cpu_baseline_saxpy(orc, seconds):
     """The CPU checker (the reference compiler's x86-64 objects when built) timed
     on this machine's cores on a bounded sample of the same workload."""
-    import oracle
-    import booth_b200 as sm
-    orc = oracle.load()
     m = 1 << 28
-    x = sm.fill_host(m, SEED + 1, 0, sm.FILL_F32_PM1, threads=orc.cores)
-    y = sm.fill_host(m, SEED + 1, 1, sm.FILL_F32_PM1, threads=orc.cores)
+    x = orc.fill(m, SEED + 1, 0, 0)
+    y = orc.fill(m, SEED + 1, 1, 0)
     orc.saxpy_inplace(y, x, 2.5)
     reps, t0 = 0, time.perf_counter()
     while True:
@@ -511,17 +751,18 @@ def cpu_baseline_saxpy(seconds):
 def run_reference(args):
     """--impl reference: the reference's own CPU implementation of the headline
     workload (its x86-64 backend's saxpy through the CPU launcher), all host
-    threads, each step a 2^28-element sample of the 2^30-element workload."""
+    threads, each step the whole 2^log2n-element vector pair of one GPU's shard.
+    Nothing of the product is loaded here: inputs come from the checker harness's
+    own generator."""
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     import oracle
-    import booth_b200 as sm
     orc = oracle.load()
-    m = 1 << 28
-    x = sm.fill_host(m, SEED + 1, 0, sm.FILL_F32_PM1, threads=orc.cores)
-    y = sm.fill_host(m, SEED + 1, 1, sm.FILL_F32_PM1, threads=orc.cores)
+    m = 1 << args.log2n
+    x = orc.fill(m, SEED + 1, 0, 0)
+    y = orc.fill(m, SEED + 1, 1, 0)
     W, K = max(args.warmup, 1), args.steps
     for _ in range(W):
         orc.saxpy_inplace(y, x, 2.5)
@@ -530,13 +771,15 @@ def run_reference(args):
         orc.saxpy_inplace(y, x, 2.5)
     dt = time.perf_counter() - t0
     gbs = 12.0 * m * K / dt / 1e9
+    sample = ("each step is one GPU's whole shard, 2^%d elements, on the host cores (%d threads over disjoint ranges)"
+              % (args.log2n, orc.cores))
     line = {"impl": "reference", "metric": "saxpy_hbm_gbs", "value": gbs, "unit": "GB/s", "n_gpus": world,
             "steps": K, "warmup": W, "ms_per_step": dt / K * 1e3, "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": "saxpy y=2.5*x+y, N=2^30 fp32 per GPU, unfused mul+add, x,y~U[-1,1) Philox-seeded",
-                       "sample": "each step is 2^28 elements of it on the host cores"},
-            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": orc.cores, "kind": orc.kind,
-                             "sample": "2^28 elements per step, %d threads over disjoint ranges" % orc.cores},
+            "config": {"workload": "saxpy y=2.5*x+y, N=2^%d fp32 per GPU, unfused mul+add, x,y~U[-1,1) Philox-seeded"
+                                   % args.log2n,
+                       "bytes_per_element": 12, "sample": sample},
+            "cpu_baseline": {"value": gbs, "unit": "GB/s", "cores": orc.cores, "kind": orc.kind, "sample": sample},
             "e2e": {"value": gbs, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     emit(line)
 
@@ -570,6 +813,8 @@ def main():
     ap.add_argument("--gemm-sizes", default=",".join(str(v) for v in GEMM_SIZES))
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-parity", action="store_true",
+                    help="skip the checks of the results against the CPU checker (they run outside the timed regions)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -97,6 +97,7 @@ _SIGNATURES = {
     "booth_sm100_saxpy": (C.c_int, [_dev, _ptr, _ptr, C.c_float, C.c_longlong]),
     "booth_sm100_vadd_host": (C.c_int, [_dev, C.c_void_p, C.c_void_p, C.c_void_p, C.c_longlong]),
     "booth_sm100_saxpy_host": (C.c_int, [_dev, C.c_void_p, C.c_void_p, C.c_float, C.c_longlong]),
+    "booth_sm100_link_probe": (C.c_int, [_dev, C.c_size_t, C.c_int, C.POINTER(C.c_double)]),
     "booth_sm100_reduce_i32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
     "booth_sm100_reduce_f32": (C.c_int, [_dev, _ptr, C.c_longlong, _ptr]),
     "booth_sm100_reduce_f32_noalloc": (C.c_int, [_ptr, C.c_longlong, _ptr, C.c_void_p]),
@@ -275,6 +276,12 @@ class Device:
 
     def vadd_host(self, x_addr, y_addr, out_addr, n):
         self._ck("booth_sm100_vadd_host", lib().booth_sm100_vadd_host(self._h, x_addr, y_addr, out_addr, n))
+
+    def link_probe(self, nbytes=1 << 30, reps=3):
+        """GB/s of the host link with pinned memory: (up alone, down alone, up and down while both run)."""
+        g = (C.c_double * 4)()
+        self._ck("booth_sm100_link_probe", lib().booth_sm100_link_probe(self._h, nbytes, reps, g))
+        return tuple(g)
 
     def reduce_i32(self, inp, n, out):
         self._ck("booth_sm100_reduce_i32", lib().booth_sm100_reduce_i32(self._h, inp, n, out))

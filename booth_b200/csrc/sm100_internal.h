@@ -98,10 +98,10 @@ struct sm100_dev {
     CUdeviceptr gemm_ws;
     size_t      gemm_ws_bytes;
     /* Host-pointer streaming (booth_sm100_*_host): a ring of device staging slots, a
-     * second stream for the copies back, and one event pair per slot. */
-    CUstream    stream_out;
+     * stream for the uploads, one for the copies back, and three events per slot. */
+    CUstream    stream_out, stream_in;
     CUdeviceptr stage;                 /* SM100_STAGE_SLOTS x 2 x SM100_STAGE_BYTES */
-    CUevent     ev_computed[SM100_STAGE_SLOTS], ev_drained[SM100_STAGE_SLOTS];
+    CUevent     ev_uploaded[SM100_STAGE_SLOTS], ev_computed[SM100_STAGE_SLOTS], ev_drained[SM100_STAGE_SLOTS];
     int         stage_ready;
     int         gemm_pending;          /* a GEMM was enqueued since the last status check */
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */

@@ -257,8 +257,11 @@ static int stage_setup(sm100_dev_t *dev)
     const sm100_api_t *a = dev->api;
     CUresult cr = a->StreamCreate(&dev->stream_out, CU_STREAM_NON_BLOCKING);
     if (cr != CUDA_SUCCESS) return sm100_fail(dev, "cuStreamCreate(copy-back stream)", cr);
+    cr = a->StreamCreate(&dev->stream_in, CU_STREAM_NON_BLOCKING);
+    if (cr != CUDA_SUCCESS) { a->StreamDestroy(dev->stream_out); return sm100_fail(dev, "cuStreamCreate(upload stream)", cr); }
     for (int i = 0; i < SM100_STAGE_SLOTS && cr == CUDA_SUCCESS; i++) {
-        cr = a->EventCreate(&dev->ev_computed[i], CU_EVENT_DISABLE_TIMING);
+        cr = a->EventCreate(&dev->ev_uploaded[i], CU_EVENT_DISABLE_TIMING);
+        if (cr == CUDA_SUCCESS) cr = a->EventCreate(&dev->ev_computed[i], CU_EVENT_DISABLE_TIMING);
         if (cr == CUDA_SUCCESS) cr = a->EventCreate(&dev->ev_drained[i], CU_EVENT_DISABLE_TIMING);
     }
     if (cr == CUDA_SUCCESS) cr = a->MemAlloc(&dev->stage, (size_t)SM100_STAGE_SLOTS * 2 * SM100_STAGE_BYTES);
@@ -268,10 +271,12 @@ static int stage_setup(sm100_dev_t *dev)
 }
 
 /* out[i] = op(x[i], y[i]) for host vectors. The vectors are cut into chunks of
- * 16 Mi elements; chunk i+1 is on its way to the device (H2D on the compute
- * stream) while chunk i is computed and chunk i-1 travels back (D2H on a second
- * stream), so both directions of the link are busy. Three staging slots of
- * 2 x 64 MiB on the device; a slot is reused once its copy back has finished. */
+ * 16 Mi elements and go through three streams: uploads (H2D of x and y) on one,
+ * the kernel on the device's own stream, copies back (D2H) on a third, chained by
+ * one event per staging slot and step. The upload of chunk i+1 therefore never
+ * queues behind the kernel of chunk i, and both directions of the link stay busy.
+ * Three staging slots of 2 x 64 MiB on the device; a slot is refilled once its
+ * copy back has finished. */
 static int stream_host(sm100_dev_t *dev, int saxpy, const float *x, const float *y, float *out, float a, long long n)
 {
     int rc = sm100_enter(dev);
@@ -283,13 +288,18 @@ static int stream_host(sm100_dev_t *dev, int saxpy, const float *x, const float 
     const long long chunk = SM100_STAGE_BYTES / 4;
     CUresult cr = CUDA_SUCCESS;
     long long done = 0;
+    /* work already queued on the device's stream (the caller's earlier calls) comes first */
+    cr = api->EventRecord(dev->ev_computed[0], dev->stream);
+    if (cr == CUDA_SUCCESS) cr = api->StreamWaitEvent(dev->stream_in, dev->ev_computed[0], 0);
     for (long long i = 0; done < n && cr == CUDA_SUCCESS; i++, done += chunk) {
         const int slot = (int)(i % SM100_STAGE_SLOTS);
         const long long m = n - done < chunk ? n - done : chunk;
         const CUdeviceptr dx = dev->stage + (size_t)slot * 2 * SM100_STAGE_BYTES, dy = dx + SM100_STAGE_BYTES;
-        if (i >= SM100_STAGE_SLOTS) cr = api->StreamWaitEvent(dev->stream, dev->ev_drained[slot], 0);
-        if (cr == CUDA_SUCCESS) cr = api->MemcpyHtoDAsync(dx, x + done, (size_t)m * 4, dev->stream);
-        if (cr == CUDA_SUCCESS) cr = api->MemcpyHtoDAsync(dy, y + done, (size_t)m * 4, dev->stream);
+        if (i >= SM100_STAGE_SLOTS) cr = api->StreamWaitEvent(dev->stream_in, dev->ev_drained[slot], 0);
+        if (cr == CUDA_SUCCESS) cr = api->MemcpyHtoDAsync(dx, x + done, (size_t)m * 4, dev->stream_in);
+        if (cr == CUDA_SUCCESS) cr = api->MemcpyHtoDAsync(dy, y + done, (size_t)m * 4, dev->stream_in);
+        if (cr == CUDA_SUCCESS) cr = api->EventRecord(dev->ev_uploaded[slot], dev->stream_in);
+        if (cr == CUDA_SUCCESS) cr = api->StreamWaitEvent(dev->stream, dev->ev_uploaded[slot], 0);
         if (cr != CUDA_SUCCESS) break;
         /* saxpy writes y in place; vector add writes its sum over the staged y */
         rc = saxpy ? booth_sm100_saxpy(dev, dy, dx, a, m) : booth_sm100_vadd(dev, dx, dy, dy, m);
@@ -299,12 +309,71 @@ static int stream_host(sm100_dev_t *dev, int saxpy, const float *x, const float 
         if (cr == CUDA_SUCCESS) cr = api->MemcpyDtoHAsync(out + done, dy, (size_t)m * 4, dev->stream_out);
         if (cr == CUDA_SUCCESS) cr = api->EventRecord(dev->ev_drained[slot], dev->stream_out);
     }
-    /* Both streams are drained on every way out: copies from x and y and into out
-     * may still be in flight, and the caller owns those buffers again on return. */
-    const CUresult d0 = api->StreamSynchronize(dev->stream_out), d1 = api->StreamSynchronize(dev->stream);
+    /* All three streams are drained on every way out: copies from x and y and into
+     * out may still be in flight, and the caller owns those buffers again on return. */
+    const CUresult d0 = api->StreamSynchronize(dev->stream_in), d1 = api->StreamSynchronize(dev->stream_out),
+                   d2 = api->StreamSynchronize(dev->stream);
     if (rc != SM100_OK) return rc;
-    if (cr == CUDA_SUCCESS) cr = d0 != CUDA_SUCCESS ? d0 : d1;
+    if (cr == CUDA_SUCCESS) cr = d0 != CUDA_SUCCESS ? d0 : d1 != CUDA_SUCCESS ? d1 : d2;
     return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "host-pointer streaming", cr);
+}
+
+/* How fast this GPU's host link moves page-locked memory: `bytes` up alone, down
+ * alone, then both at once on two streams, each repeated `reps` times; GB/s. */
+int booth_sm100_link_probe(sm100_dev_t *dev, size_t bytes, int reps, double gbs[4])
+{
+    int rc = sm100_enter(dev);
+    if (rc != SM100_OK) return rc;
+    if (!gbs || bytes < 4096 || reps < 1) return bad_arg(dev, "booth_sm100_link_probe: bad argument");
+    if ((rc = stage_setup(dev)) != SM100_OK) return rc;
+    const sm100_api_t *api = dev->api;
+    void *hup = NULL, *hdn = NULL;
+    CUdeviceptr dup = 0, ddn = 0;
+    CUevent e0 = NULL, e1 = NULL, f0 = NULL, f1 = NULL;
+    CUresult cr = api->MemHostAlloc(&hup, bytes, CU_MEMHOSTALLOC_PORTABLE);
+    if (cr == CUDA_SUCCESS) cr = api->MemHostAlloc(&hdn, bytes, CU_MEMHOSTALLOC_PORTABLE);
+    if (cr == CUDA_SUCCESS) cr = api->MemAlloc(&dup, bytes);
+    if (cr == CUDA_SUCCESS) cr = api->MemAlloc(&ddn, bytes);
+    if (cr == CUDA_SUCCESS) cr = api->EventCreate(&e0, CU_EVENT_DEFAULT);
+    if (cr == CUDA_SUCCESS) cr = api->EventCreate(&e1, CU_EVENT_DEFAULT);
+    if (cr == CUDA_SUCCESS) cr = api->EventCreate(&f0, CU_EVENT_DEFAULT);
+    if (cr == CUDA_SUCCESS) cr = api->EventCreate(&f1, CU_EVENT_DEFAULT);
+    if (cr == CUDA_SUCCESS) { memset(hup, 1, bytes); memset(hdn, 0, bytes); }
+    if (cr == CUDA_SUCCESS) cr = api->StreamSynchronize(dev->stream);
+    for (int mode = 0; mode < 3 && cr == CUDA_SUCCESS; mode++) {          /* up, down, both */
+        for (int r = -1; r < reps && cr == CUDA_SUCCESS; r++) {           /* r = -1: untimed warm-up */
+            if (r == 0) {
+                cr = api->EventRecord(e0, dev->stream_in);
+                if (cr == CUDA_SUCCESS) cr = api->EventRecord(f0, dev->stream_out);
+            }
+            if (cr == CUDA_SUCCESS && mode != 1) cr = api->MemcpyHtoDAsync(dup, hup, bytes, dev->stream_in);
+            if (cr == CUDA_SUCCESS && mode != 0) cr = api->MemcpyDtoHAsync(hdn, ddn, bytes, dev->stream_out);
+            if (r == -1 && cr == CUDA_SUCCESS) {
+                cr = api->StreamSynchronize(dev->stream_in);
+                if (cr == CUDA_SUCCESS) cr = api->StreamSynchronize(dev->stream_out);
+            }
+        }
+        if (cr == CUDA_SUCCESS) cr = api->EventRecord(e1, dev->stream_in);
+        if (cr == CUDA_SUCCESS) cr = api->EventRecord(f1, dev->stream_out);
+        if (cr == CUDA_SUCCESS) cr = api->StreamSynchronize(dev->stream_in);
+        if (cr == CUDA_SUCCESS) cr = api->StreamSynchronize(dev->stream_out);
+        float up_ms = 0.0f, dn_ms = 0.0f;
+        if (cr == CUDA_SUCCESS) cr = api->EventElapsedTime(&up_ms, e0, e1);
+        if (cr == CUDA_SUCCESS) cr = api->EventElapsedTime(&dn_ms, f0, f1);
+        const double vol = (double)bytes * reps / 1e9;
+        if (mode == 0) gbs[0] = up_ms > 0 ? vol / (up_ms * 1e-3) : 0.0;
+        if (mode == 1) gbs[1] = dn_ms > 0 ? vol / (dn_ms * 1e-3) : 0.0;
+        if (mode == 2) { gbs[2] = up_ms > 0 ? vol / (up_ms * 1e-3) : 0.0; gbs[3] = dn_ms > 0 ? vol / (dn_ms * 1e-3) : 0.0; }
+    }
+    if (e0) api->EventDestroy(e0);
+    if (e1) api->EventDestroy(e1);
+    if (f0) api->EventDestroy(f0);
+    if (f1) api->EventDestroy(f1);
+    if (dup) api->MemFree(dup);
+    if (ddn) api->MemFree(ddn);
+    if (hup) api->MemFreeHost(hup);
+    if (hdn) api->MemFreeHost(hdn);
+    return cr == CUDA_SUCCESS ? SM100_OK : sm100_fail(dev, "link probe", cr);
 }
 
 int booth_sm100_saxpy_host(sm100_dev_t *dev, float *y, const float *x, float a, long long n)

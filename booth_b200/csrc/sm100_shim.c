@@ -261,8 +261,12 @@ void sm100_rt_shut(sm100_dev_t *dev)
         a->StreamSynchronize(dev->stream);
         if (dev->stage_ready) {
             a->StreamSynchronize(dev->stream_out);
-            for (int i = 0; i < SM100_STAGE_SLOTS; i++) { a->EventDestroy(dev->ev_computed[i]); a->EventDestroy(dev->ev_drained[i]); }
+            a->StreamSynchronize(dev->stream_in);
+            for (int i = 0; i < SM100_STAGE_SLOTS; i++) {
+                a->EventDestroy(dev->ev_uploaded[i]); a->EventDestroy(dev->ev_computed[i]); a->EventDestroy(dev->ev_drained[i]);
+            }
             a->StreamDestroy(dev->stream_out);
+            a->StreamDestroy(dev->stream_in);
             a->MemFree(dev->stage);
         }
         if (dev->gemm_ws) a->MemFree(dev->gemm_ws);

@@ -171,14 +171,21 @@ int  booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y,
 int  booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x,
                        float a, long long n);
 /* The same two operations on HOST vectors: chunks of 16 Mi elements are copied
- * in, computed and copied back in a three-slot pipeline on two streams, so the
- * host-to-device and device-to-host directions of the link overlap. These calls
+ * in, computed and copied back in a three-slot pipeline on three streams (uploads,
+ * kernels, copies back), so the host-to-device and device-to-host directions of
+ * the link overlap and no upload queues behind a kernel. These calls
  * return when the result is in host memory. Page-locked host memory
  * (sm100_rt_hostalloc) runs at link speed; pageable memory works, staged by the
  * driver. They are what the CPU-launcher symbols vector_add and saxpy call
  * (examples/cpu_launch_vadd.c:35 hands host arrays to the kernel). */
 int  booth_sm100_vadd_host(sm100_dev_t *dev, const float *x, const float *y, float *out, long long n);
 int  booth_sm100_saxpy_host(sm100_dev_t *dev, float *y, const float *x, float a, long long n);
+/* Measures the host link of this GPU with page-locked memory it allocates itself:
+ * gbs[0] host-to-device alone, gbs[1] device-to-host alone, gbs[2] and gbs[3] the
+ * two directions while both run at once (GB/s; `bytes` per copy, `reps` copies per
+ * figure after one warm-up). The ceiling the *_host calls above can reach is
+ * what this reports. No counterpart in the reference. */
+int  booth_sm100_link_probe(sm100_dev_t *dev, size_t bytes, int reps, double gbs[4]);
 /* Sum of n int32 with wrapping arithmetic into *out (one int32 on the device):
  * the tg_reduce / reduce_sum shape, tests/tg_reduce.cu:4-26,
  * tests/canonical.cu:59-108. For both sums in must be 4-byte aligned and out

@@ -136,6 +136,59 @@ def test_reference_example_programs_relinked(sm, prog, needs_cubin, expect):
     assert expect in res.stdout
 
 
+@pytest.mark.parametrize("target", [["--target", "sm100"], []])
+def test_reference_booth_run_launches_saxpy_on_the_b200(sm, oracle_lib, tmp_path, target):
+    """Row "rt_desc_t registration": the reference's own command line
+    (src/exec/booth_run.c:262-313, compiled unchanged; src/exec/execs.c with
+    rt_list = { &rt_sm100, NULL }, its documented one-line edit) loads the cubin,
+    stages the files, launches saxpy with the geometry given on the command line,
+    and writes y back: bit-identical to the CPU checker. With --target and with the
+    probing form (rt_open(NULL) takes the first target that has a device)."""
+    exe = os.path.join(EXAMPLES, "booth-run")
+    if not os.path.exists(exe):
+        pytest.skip("build/examples/booth-run was not built (the reference tree was absent at build time)")
+    n = 1024
+    x = sm.fill_host(n, 0xB0070001, 0, 0)
+    y = sm.fill_host(n, 0xB0070001, 1, 0)
+    x.tofile(tmp_path / "x.bin"); y.tofile(tmp_path / "y.bin")
+    cmd = [exe, sm.CUBIN_PATH, "saxpy"] + target + ["--grid", "4", "--block", "256", "io:%s" % (tmp_path / "y.bin"),
+                                                    "in:%s" % (tmp_path / "x.bin"), "f32:2.5", "u32:%d" % n]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert "wrote %s (%d bytes)" % (tmp_path / "y.bin", 4 * n) in res.stdout
+    got = np.fromfile(tmp_path / "y.bin", np.float32)
+    assert np.array_equal(got.view(np.uint32), oracle_lib.saxpy(y, x, 2.5).view(np.uint32))
+    # teeth: the file really changed, and a wrong scalar gives another answer
+    assert not np.array_equal(got, y)
+    # out: form and a vector add by name, block count chosen by the caller (a ragged size)
+    m = 1000
+    out = tmp_path / "c.bin"
+    x[:m].tofile(tmp_path / "a.bin"); y[:m].tofile(tmp_path / "b.bin")
+    cmd = [exe, sm.CUBIN_PATH, "vector_add"] + target + ["--grid", "3", "--block", "128,2", "in:%s" % (tmp_path / "a.bin"),
+                                                         "in:%s" % (tmp_path / "b.bin"), "out:%s:%d" % (out, 4 * m),
+                                                         "i32:%d" % m, "i32:256"]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert res.returncode == 0, res.stdout + res.stderr
+    assert np.array_equal(np.fromfile(out, np.float32).view(np.uint32), oracle_lib.vadd(x[:m].copy(), y[:m].copy()).view(np.uint32))
+
+
+def test_reference_differential_harness_relinked(sm):
+    """The reference's own parity program (tests/diff/diff_vadd.c with bc_diff.h and
+    vadd_io.h, compiled unchanged, linked against libbooth_sm100 in place of the
+    kernel object its compiler emits): clean run PASSes, --inject FAILs, as
+    tests/diff/run_diff.sh:32-44 demands of every backend. And tests/build/run_vadd.c,
+    the same idea for the BIR kernel vadd(a, b, c, n, nthreads)."""
+    exe = os.path.join(EXAMPLES, "diff_vadd")
+    if not os.path.exists(exe):
+        pytest.skip("build/examples/diff_vadd was not built (the reference tree was absent at build time)")
+    clean = subprocess.run([exe], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert clean.returncode == 0 and "PASS" in clean.stdout, clean.stdout + clean.stderr
+    inject = subprocess.run([exe, "--inject"], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert inject.returncode != 0 and "FAIL" in inject.stdout, inject.stdout + inject.stderr
+    res = subprocess.run([os.path.join(EXAMPLES, "run_vadd")], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=120)
+    assert res.returncode == 0 and "all 16 elements correct" in res.stdout, res.stdout + res.stderr
+
+
 def test_reference_sysprint_demo_relinked(sm):
     """A second consumer of the bc_* API: the reference's SYSPRINT demo
     (examples/launch_sysprint.c, runtime/sysprint.c) built unchanged against this

@@ -101,24 +101,31 @@ def test_gemm_any_size(sm, dev, oracle_lib, M, N, K):
         dev.free(p)
 
 
-@pytest.mark.parametrize("size", [4096, 8192])
-def test_gemm_full_size_sampled_rows(sm, dev, oracle_lib, size):
-    """M = N = K in {4096, 8192}: inputs generated on the device from the seeded
-    stream, the CPU checker computes a seeded sample of 4-row blocks of C from
-    the same stream generated on the host (rows of C are independent given B)."""
-    M = N = K = size
+@pytest.mark.parametrize("M,size", [(4096, 4096), (8192, 8192), (512, 4096), (1024, 8192)])
+def test_gemm_full_size_sampled_rows(sm, dev, oracle_lib, M, size):
+    """N = K in {4096, 8192} with M = N (one GPU) and with the row blocks one of
+    eight GPUs holds (512 x 4096 x 4096, 1024 x 8192 x 8192; the second of them, so
+    A starts at row M of the global matrix): inputs generated on the device from the
+    seeded stream, the CPU checker computes a seeded sample of 64 four-row blocks
+    (256 rows) of C from the same stream generated on the host (rows of C are
+    independent given B)."""
+    N = K = size
+    row0 = 0 if M == size else M                       # the shard's first row of the global A
     da, db, dc = dev.alloc(M * K * 4), dev.alloc(K * N * 4), dev.alloc(M * N * 4)
-    dev.fill(da, 0, M * K, 0xB0070003, 0, 0)
+    dev.fill(da, row0 * K, M * K, 0xB0070003, 0, 0)
     dev.fill(db, 0, K * N, 0xB0070003, 1, 0)
+    dev.zero(dc, M * N * 4)
     dev.gemm(dc, da, db, M, N, K)
     dev.sync()
-    rng = np.random.default_rng(size)
-    rows4 = np.sort(rng.choice(M // 4, size=32 if size == 8192 else 64, replace=False)).astype(np.int32)
-    a, b = inputs(sm, M, N, K)
-    want = oracle_lib.matmul(a, b, rows4=rows4)
-    rows = (rows4[:, None] * 4 + np.arange(4)[None, :]).ravel()
-    got = np.stack([dev.download(dc + int(r) * N * 4, N, np.float32) for r in rows])
-    assert rel_fro(got, want[rows]) <= TOL
+    rng = np.random.default_rng(size + M)
+    rows4 = np.sort(rng.choice(M // 4, size=64, replace=False)).astype(np.int32)
+    b = sm.fill_host(K * N, 0xB0070003, 1, 0, threads=16).reshape(K, N)
+    a = np.concatenate([sm.fill_host(4 * K, 0xB0070003, 0, 0, first=(row0 + 4 * int(r)) * K) for r in rows4]).reshape(256, K)
+    want = oracle_lib.matmul(a, b)
+    got = np.concatenate([dev.download(dc + 4 * int(r) * N * 4, (4, N), np.float32) for r in rows4])
+    assert rel_fro(got, want) <= TOL
+    # teeth: the same comparison notices one row block of C shifted by one block
+    assert rel_fro(np.roll(got, 4, axis=0), want) > 100 * TOL
     for p in (da, db, dc):
         dev.free(p)
 

@@ -392,7 +392,7 @@ def test_bench_line_keeps_its_contract_over_the_fake(fake, fake_nccl, tmp_path):
     import json
     env = dict(os.environ, BOOTH_CUDA_LIB=fake, BOOTH_NCCL_LIB=fake_nccl, PYTHONPATH=ROOT)
     res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--log2n", "16", "--log2paths", "10", "--gemm-sizes", "256",
-                          "--steps", "4", "--warmup", "3", "--cpu-seconds", "0.05"], cwd=ROOT, env=env,
+                          "--steps", "4", "--warmup", "3", "--cpu-seconds", "0.05", "--no-parity"], cwd=ROOT, env=env,
                          stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
     assert res.returncode == 0, res.stderr[-2000:]
     out = [ln for ln in res.stdout.splitlines() if ln.strip()]
@@ -410,6 +410,32 @@ def test_bench_line_keeps_its_contract_over_the_fake(fake, fake_nccl, tmp_path):
     assert "workload" in j["config"] and "model" not in j["config"]
     names = [w["name"] for w in j["workloads"]]
     assert any(n.startswith("gemm") for n in names) and any(n.startswith("asian") for n in names)
+    assert j["parity"] is None                                   # switched off above: the fake computes nothing
+    assert j["e2e"]["roofline"]["bound"] == "pcie" and set(j["e2e"]["roofline"]["link_gbs"]) == {"h2d", "d2h", "h2d_duplex", "d2h_duplex"}
+    for w in j["workloads"]:                                     # every measured workload carries its own e2e and roofline
+        if "value" in w:
+            assert "roofline" in w and set(w["e2e"]) >= {"value", "unit", "h2d_bytes_per_step", "d2h_bytes_per_step"}, w["name"]
+    mc = [w for w in j["workloads"] if w["name"].startswith("asian_mc_fast")][0]
+    assert mc["roofline"]["bound"] == "mufu issue" and mc["second_bound"]["bound"] == "warp instruction issue"
+
+
+def test_bench_parity_block_has_teeth(fake, fake_nccl, tmp_path):
+    """bench.py checks every workload's result against the CPU checker outside the
+    timed regions and exits non-zero on a miss. Over the fake driver nothing is
+    computed, so every check must miss: the line still comes out, says which, and
+    the exit status is 3."""
+    import json
+    env = dict(os.environ, BOOTH_CUDA_LIB=fake, BOOTH_NCCL_LIB=fake_nccl, PYTHONPATH=ROOT)
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--log2n", "16", "--log2paths", "10", "--gemm-sizes", "256",
+                          "--steps", "2", "--warmup", "3", "--no-cpu-baseline", "--no-e2e"], cwd=ROOT, env=env,
+                         stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=600)
+    assert res.returncode == 3, res.stderr[-2000:]
+    j = json.loads([ln for ln in res.stdout.splitlines() if ln.strip()][0])
+    par = j["parity"]
+    assert par["status"].startswith("MISS") and par["checker"] in ("reference", "port")
+    for key in ("saxpy_mismatches", "int32", "fp32_rel", "mc_rel_fast", "mc_rel_precise", "gemm_rel_fro_256"):
+        assert key in par and key in par["status"], key
+    assert par["saxpy_mismatches"] > 0 and "PARITY MISS" in res.stderr
 
 
 def test_reference_arm_line_needs_no_gpu(tmp_path):
@@ -418,7 +444,8 @@ def test_reference_arm_line_needs_no_gpu(tmp_path):
     one JSON line, no driver touched."""
     import json
     env = dict(os.environ, BOOTH_CUDA_LIB="/nonexistent/libcuda.so.1", PYTHONPATH=ROOT)
-    res = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1", "--warmup", "1"],
+    res = subprocess.run([sys.executable, "-X", "importtime", os.path.join(ROOT, "bench.py"), "--impl", "reference", "--steps", "1",
+                          "--warmup", "1", "--log2n", "24"],
                          cwd=ROOT, env=env, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True, timeout=900)
     assert res.returncode == 0, res.stderr[-2000:]
     out = [ln for ln in res.stdout.splitlines() if ln.strip()]
@@ -429,7 +456,9 @@ def test_reference_arm_line_needs_no_gpu(tmp_path):
     assert j["cpu_baseline"]["kind"] in ("reference", "port") and j["cpu_baseline"]["cores"] >= 1
     assert j["cpu_baseline"]["value"] == j["value"] == j["e2e"]["value"]
     assert j["e2e"]["h2d_bytes_per_step"] == 0 and j["e2e"]["d2h_bytes_per_step"] == 0
-    assert "N=2^30" in j["config"]["workload"]
+    assert "N=2^24" in j["config"]["workload"]                   # the default is the GPU arm's 2^30
+    # nothing of the product is loaded in this arm: no import of the package, no libbooth_sm100
+    assert "booth_b200" not in res.stderr and "oracle" in res.stderr
 
 
 def test_two_rank_bench_path_over_the_fakes(fake, fake_nccl, tmp_path):
@@ -442,7 +471,7 @@ def test_two_rank_bench_path_over_the_fakes(fake, fake_nccl, tmp_path):
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                           "--master-addr", "127.0.0.1", "--master-port", "29541", os.path.join(ROOT, "bench.py"),
                           "--gpus", "2", "--log2n", "16", "--log2paths", "10", "--gemm-sizes", "256", "--steps", "3",
-                          "--warmup", "3", "--no-cpu-baseline"], cwd=ROOT, env=env, stdout=subprocess.PIPE,
+                          "--warmup", "3", "--no-cpu-baseline", "--no-parity"], cwd=ROOT, env=env, stdout=subprocess.PIPE,
                          stderr=subprocess.PIPE, text=True, timeout=900)
     assert res.returncode == 0, res.stderr[-3000:]
     out = [ln for ln in res.stdout.splitlines() if ln.strip().startswith("{")]

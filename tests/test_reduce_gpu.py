@@ -108,3 +108,20 @@ def test_full_size_2_30(sm, dev, oracle_lib):
     assert abs(np.float32(got_f) - np.float32(want)) <= REL * abs(want)
     assert abs(got_f - truth) <= REL * abs(truth)
     dev.free(p)
+
+
+def test_bad_addresses_are_refused_on_the_host(sm, dev):
+    """A result address that is not aligned to the result's size, or a NULL input
+    with n > 0, would fault on the device; the calls return SM100_ERR_ARG before
+    any GPU work and the device stays usable."""
+    x, out = dev.alloc(4096), dev.alloc(64)
+    L = sm.lib()
+    assert L.booth_sm100_reduce_f32(dev.handle, x, 100, out + 4) == sm.ERR_ARG
+    assert L.booth_sm100_reduce_i32(dev.handle, x, 100, out + 2) == sm.ERR_ARG
+    assert L.booth_sm100_reduce_f32(dev.handle, 0, 100, out) == sm.ERR_ARG
+    assert L.booth_sm100_reduce_i32(dev.handle, x + 1, 100, out) == sm.ERR_ARG
+    assert L.booth_sm100_asian(dev.handle, sm.asian_params(), 0, 1000, out + 4) == sm.ERR_ARG
+    dev.zero(x, 4096)
+    dev.reduce_i32(x, 1024, out + 4)                     # 4-byte alignment is enough for the int32 sum
+    assert int(dev.download(out + 4, 1, np.int32)[0]) == 0
+    dev.free(x); dev.free(out)

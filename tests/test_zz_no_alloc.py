@@ -66,6 +66,10 @@ def test_sizes_beyond_the_built_in_scratch_are_refused(sm, dev):
     assert L.booth_sm100_reduce_f32_noalloc(p, (1 << 30) + 1, out, None) == sm.ERR_ARG
     assert L.booth_sm100_reduce_f32_noalloc(p, -1, out, None) == sm.ERR_ARG
     assert L.booth_sm100_reduce_f32_noalloc(p, 16, 0, None) == sm.ERR_ARG
+    # a result address that is not 8-byte aligned would fault on the device: refused on the host
+    assert L.booth_sm100_reduce_f32_noalloc(p, 16, out + 4, None) == sm.ERR_ARG
+    assert L.booth_sm100_reduce_f32_noalloc(p + 2, 16, out, None) == sm.ERR_ARG
+    assert L.booth_sm100_reduce_f32_noalloc(0, 16, out, None) == sm.ERR_ARG
     dev.free(p); dev.free(out)
 
 
