@@ -263,6 +263,42 @@ def roofline(bound, achieved, peak, unit, traffic, peaks):
     return r
 
 
+def host_placement(index):
+    """Where this rank's GPU hangs off the host, read from sysfs (nothing is changed
+    except this process's own CPU affinity): when the GPU's PCI device names a NUMA
+    node and a CPU list, the process (and with it the threads that fill and touch
+    the page-locked buffers) is kept on those CPUs, so that staging memory is
+    allocated next to the GPU. Returns what was found for the JSON line."""
+    info = {"numa_node": None, "bound_to_local_cpus": False}
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        bus = pynvml.nvmlDeviceGetPciInfo(pynvml.nvmlDeviceGetHandleByIndex(index)).busId
+        bus = (bus.decode() if isinstance(bus, bytes) else bus).lower()
+        if len(bus.split(":")[0]) == 8:
+            bus = bus[4:]
+        base = os.path.join("/sys/bus/pci/devices", bus)
+        with open(os.path.join(base, "numa_node")) as f:
+            info["numa_node"] = int(f.read().strip())
+        with open(os.path.join(base, "local_cpulist")) as f:
+            text = f.read().strip()
+        info["local_cpulist"] = text
+        cpus = set()
+        for part in text.split(","):
+            if "-" in part:
+                lo, hi = part.split("-")
+                cpus.update(range(int(lo), int(hi) + 1))
+            elif part:
+                cpus.add(int(part))
+        allowed = os.sched_getaffinity(0)
+        if info["numa_node"] is not None and info["numa_node"] >= 0 and cpus and cpus & allowed and (cpus & allowed) != allowed:
+            os.sched_setaffinity(0, cpus & allowed)
+            info["bound_to_local_cpus"] = True
+    except Exception as e:
+        info["note"] = "not available: %s" % type(e).__name__
+    return info
+
+
 def wall(ranks, steps, body):
     """End-to-end timing of a host-buffer call: one untimed call, then `steps`
     calls on the wall clock between barriers (each call returns with its result in
@@ -286,6 +322,9 @@ def run_ours(args):
     import booth_b200 as sm
     ranks = Ranks(args.gpus)
     peaks = measured_peaks()
+    # With several ranks on one host, keep each next to its own GPU before any staging
+    # memory is allocated. A 1-GPU run keeps all cores (they time the CPU baseline).
+    placement = host_placement(ranks.local) if ranks.world > 1 else {"bound_to_local_cpus": False, "note": "single rank: all cores kept"}
     dev = sm.Device(ranks.local)
     comm = None
     if ranks.world > 1:
@@ -346,7 +385,7 @@ def run_ours(args):
         dev.fill(dy, first, n, SEED + 1, 1, sm.FILL_F32_PM1)
 
     # ---- e2e: host buffers in, result back in host memory, through the library's calls ----
-    e2e = None if args.no_e2e else run_e2e_saxpy(sm, dev, ranks, n, Ke)
+    e2e = None if args.no_e2e else run_e2e_saxpy(sm, dev, ranks, n, Ke, placement)
     want = set(args.workloads.split(",")) if args.workloads != "all" else {"sweep", "vadd", "reduce", "asian", "gemm"}
     if args.headline_only:
         want = set()
@@ -532,7 +571,7 @@ def run_ours(args):
         raise SystemExit(3)
 
 
-def run_e2e_saxpy(sm, dev, ranks, n, steps):
+def run_e2e_saxpy(sm, dev, ranks, n, steps, placement):
     """The headline workload end to end: pinned host x and y go to the device, y
     comes back, every byte counted. Two forms: the pipelined host-vector call
     (booth_sm100_saxpy_host, the figure), and the synchronous bc_* flow of the
@@ -580,9 +619,13 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps):
     ranks.barrier()
     up, down, up2, down2 = dev.link_probe(min(1 << 30, max(nbytes, 1 << 16)), 3)
     ranks.barrier()
-    # 2 bytes go up for every byte that comes down; with both directions busy the call
-    # cannot end before the slower of (8n / up-rate) and (4n / down-rate).
-    bound_s = max(2.0 * nbytes / (up2 * 1e9), 1.0 * nbytes / (down2 * 1e9)) if up2 > 0 and down2 > 0 else None
+    # 2 bytes go up for every byte that comes down, so the call cannot end before the
+    # upload alone would: 8N bytes at the host-to-device rate this link reaches when it
+    # has the link to itself (the ceiling), nor, more tightly, before the slower of the
+    # two directions at the rates they reach while BOTH stream flat out (a 1:1 mix,
+    # harder on the link than this call's 2:1, so that second figure can be beaten).
+    bound_s = max(2.0 * nbytes / (up * 1e9), 1.0 * nbytes / (down * 1e9)) if up > 0 and down > 0 else None
+    duplex_s = max(2.0 * nbytes / (up2 * 1e9), 1.0 * nbytes / (down2 * 1e9)) if up2 > 0 and down2 > 0 else None
     peak = 12.0 * n / bound_s / 1e9 if bound_s else None
     mine = 12.0 * n * steps / per_rank[ranks.rank] / 1e9
     fracs = ranks.gather(mine / peak if peak else 0.0)
@@ -593,11 +636,14 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps):
                    "on three streams; returns with y in host memory",
             "roofline": {"bound": "pcie", "unit": "GB/s", "achieved": mine, "peak": peak,
                          "frac": mine / peak if peak else None,
-                         "peak_source": "measured in this run on rank 0's GPU (booth_sm100_link_probe, 3 x 1 GiB pinned copies): "
-                                        "H2D %.1f, D2H %.1f alone; %.1f and %.1f with both directions busy; peak = 12 B x N / "
-                                        "max(8N/up, 4N/down)" % (up, down, up2, down2),
+                         "peak_source": "measured in this run on this rank's GPU while every rank measures its own "
+                                        "(booth_sm100_link_probe, 3 x 1 GiB pinned copies): H2D %.1f, D2H %.1f GB/s alone; "
+                                        "%.1f and %.1f with both directions flat out; peak = 12 B x N / max(8N/H2D, 4N/D2H) "
+                                        "from the rates alone" % (up, down, up2, down2),
+                         "peak_both_directions_flat_out": 12.0 * n / duplex_s / 1e9 if duplex_s else None,
                          "link_gbs": {"h2d": up, "d2h": down, "h2d_duplex": up2, "d2h_duplex": down2},
                          "frac_per_rank": fracs},
+            "host": placement,
             "per_rank_s": per_rank,
             "launcher_api": launcher}
 

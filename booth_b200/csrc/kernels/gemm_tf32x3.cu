@@ -127,6 +127,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32])
                  : "r"(taddr));
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+
 __device__ __forceinline__ float to_tf32(float x)
 {
     uint32_t r;
@@ -258,7 +267,9 @@ __device__ __forceinline__ void zero_tile_part(float *__restrict__ c, int M, int
 //   blocks [0, a_blocks)                     split A into its hi/lo planes;
 //   blocks [a_blocks, a_blocks + b_blocks)   split and transpose 64 x 64 tiles of B
 //                                            (b_blocks = 0 when the planes of B are kept);
-//   the last n_zero blocks                   zero the tiles of C that two clusters share.
+//   the last n_zero blocks                   zero the tiles of C that two clusters share
+//                                            (one-tile-per-cluster contraction only);
+//   block 0 also clears the nflags counters of the persistent contraction.
 // The parts are independent and all bound by HBM, so they stream side by side.
 // Launched with programmatic stream serialization: the grid is set up while the
 // previous kernel on the stream drains, waits for that kernel's memory (it may
@@ -267,12 +278,15 @@ __device__ __forceinline__ void zero_tile_part(float *__restrict__ c, int M, int
 extern "C" __global__ void __launch_bounds__(256)
 gemm_prepass(const float *__restrict__ a, float4 *__restrict__ a_hi, float4 *__restrict__ a_lo, int M, int K, int Mp, int Kp,
              const float *__restrict__ b, float *__restrict__ b_hi, float *__restrict__ b_lo, int N, int Np,
-             float *__restrict__ c, int tiles_n, int tile_from, unsigned a_blocks, unsigned b_blocks)
+             float *__restrict__ c, int tiles_n, int tile_from, unsigned a_blocks, unsigned b_blocks,
+             unsigned *__restrict__ flags, unsigned nflags)
 {
     __shared__ float tile[64][65];            // [k][n], used by the B part
     asm volatile("griddepcontrol.wait;" ::: "memory");
     asm volatile("griddepcontrol.launch_dependents;");
     const unsigned blk = blockIdx.x;
+    // the persistent contraction's "partial sums ready" counters start every call at zero
+    if (blk == 0) for (unsigned i = threadIdx.x; i < nflags; i += 256) flags[i] = 0u;
     if (blk < a_blocks) {
         gemm::split_a_part(a, a_hi, a_lo, M, K, Mp, Kp, blk, a_blocks);
     } else if (blk < a_blocks + b_blocks) {
@@ -727,4 +741,273 @@ gemm_tf32x3_2cta_n128(const __grid_constant__ CUtensorMap map_a_hi, const __grid
                  int silent_producer)
 {
     gemm_pair_tile<128, 4>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, split_from, status, wait_ns, silent_producer);
+}
+
+
+// ---------------------------------------------------------------------------
+// Persistent two-CTA form: one cluster per SM pair for the whole GEMM.
+//
+// The grid is 2 x C CTAs, C = the number of CTA pairs the GPU holds at once, and
+// every cluster walks a list of work items instead of exiting after one tile:
+//   * full waves: cluster cl computes tiles cl, cl + C, cl + 2C, ... over all of K
+//     (the clusters of a wave run in step, so the ~C tiles in flight keep sharing
+//     their A and B panels through L2 as in the one-tile-per-cluster form);
+//   * the tail (tiles % C tiles that would leave most pairs idle): its K chunks are
+//     dealt out evenly, cluster cl takes chunks [cl*U/C, (cl+1)*U/C) of the U chunks
+//     of all tail tiles, so a tail tile may be shared by two or more clusters. The
+//     cluster that holds a tile's first chunk owns the tile: the others write their
+//     partial sums to a per-cluster slot of the workspace and raise a flag, the
+//     owner adds them to its own sum in cluster order and stores C. A partial is
+//     always the FIRST thing its cluster does in the tail and the owner asks for
+//     it LAST, so no cluster ever waits for work that waits for it; the wait is
+//     bounded like every other wait here. No atomics on C, no zeroed C, and the
+//     sum does not depend on timing.
+// Staying resident saves the per-tile set-up (barriers, tensor memory) and lets
+// the tensor pipe start the next item's first chunks while the eight epilogue
+// warps still store the previous tile.
+//
+// 384 threads: warp 0 TMA producer, warp 1 MMA issuer (and tensor-memory
+// allocation), warps 4-11 running sum + epilogue (warp w reads TMEM lanes
+// 32*(w%4)..; warps 4-7 the left half of the columns, 8-11 the right half).
+namespace gemm {
+
+struct WorkItem { int tile, c0, c1; };          // chunks [c0, c1) of K for this tile
+
+struct Schedule {
+    int C, cl, nck, nfull, rem, split;
+    long long u0, u1;                           // this cluster's chunks of the tail
+    int w;                                      // iteration state
+    long long u;
+    __device__ __forceinline__ Schedule(int C_, int cl_, int tiles, int nck_, int split_)
+        : C(C_), cl(cl_), nck(nck_), nfull(tiles / C_), rem(tiles % C_), split(split_)
+    {
+        const long long U = (long long)rem * nck;
+        u0 = split ? (long long)cl * U / C : 0;
+        u1 = split ? (long long)(cl + 1) * U / C : 0;
+        w = 0; u = u0;
+    }
+    __device__ __forceinline__ long long tail_begin(int j) const { return (long long)j * ((long long)rem * nck) / C; }
+    __device__ __forceinline__ bool next(WorkItem &it)
+    {
+        if (w < nfull) { it.tile = w * C + cl; it.c0 = 0; it.c1 = nck; w++; return true; }
+        if (!split) {
+            if (w == nfull && cl < rem) { it.tile = nfull * C + cl; it.c0 = 0; it.c1 = nck; w++; return true; }
+            return false;
+        }
+        if (u < u1) {
+            const long long t = u / nck;
+            it.tile = nfull * C + (int)t;
+            it.c0 = (int)(u - t * nck);
+            const long long left = u1 - u;
+            const int room = nck - it.c0;
+            it.c1 = it.c0 + (int)(left < room ? left : room);
+            u += it.c1 - it.c0;
+            return true;
+        }
+        return false;
+    }
+};
+
+// Bounded wait for a counter in global memory to reach `target`.
+__device__ __forceinline__ bool flag_wait(const unsigned *flag, unsigned target, const WaitCtl &w, int code)
+{
+    const unsigned long long t0 = globaltimer();
+    for (;;) {
+        unsigned v;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flag) : "memory");
+        if (v >= target) return true;
+        if (globaltimer() - t0 > w.limit_ns) { atomicCAS(w.status, 0, code); return false; }
+        __nanosleep(256);
+    }
+}
+
+constexpr int PARTIAL_FLOATS = 2 * 8 * 128 * 32;     // one cluster's slot: [cta][epilogue warp][column][lane]
+
+}  // namespace gemm
+
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
+gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                    float *__restrict__ c, int M, int N, int Np, int K, int tail_split,
+                    int *status_word, unsigned long long wait_ns, int silent_producer,
+                    float *__restrict__ partial_ws, unsigned *__restrict__ flags)
+{
+    using namespace gemm;
+    constexpr int BN = 256, STAGES = 3, HALF_N = BN / 2, HALF = BN / 2, CHUNK_KB = 4;
+    constexpr uint32_t A_BYTES = BM * BK * 4, B_BYTES = HALF_N * BK * 4;
+    constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + 2 * B_BYTES;          // per CTA
+    constexpr uint32_t TMEM_COLS = 2 * BN;
+    const WaitCtl status = { status_word, wait_ns };
+
+    extern __shared__ uint8_t smem_persist[];
+    __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
+    __shared__ uint32_t s_tmem;
+
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const uint32_t smem0 = (smem_u32(smem_persist) + 1023u) & ~1023u;
+    const uint32_t full0 = smem_u32(&bars[0]), empty0 = smem_u32(&bars[STAGES]);
+    const uint32_t acc_full0 = smem_u32(&bars[2 * STAGES]), acc_empty0 = smem_u32(&bars[2 * STAGES + 2]);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tiles_m = (M + 255) / 256, tiles_n = Np / BN;
+    const int nkb = K / BK, nck = (nkb + CHUNK_KB - 1) / CHUNK_KB;
+    const int C = (int)(gridDim.x >> 1), cl = (int)(blockIdx.x >> 1);
+    Schedule sched(C, cl, tiles_m * tiles_n, nck, tail_split);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, 1); }
+        for (int b = 0; b < 2; b++) { mbar_init(acc_full0 + 8 * b, 1); mbar_init(acc_empty0 + 8 * b, 16); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncwarp();
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&s_tmem)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem = s_tmem;
+    asm volatile("griddepcontrol.wait;" ::: "memory");       // the planes, the flags and C are touched only from here on
+    asm volatile("griddepcontrol.launch_dependents;");
+
+    if (warp == 0) {
+        // ---- TMA producer, one lane in each CTA; completions count on the leader's barrier ----
+        if (lane == 0 && !silent_producer) {
+            uint32_t it = 0;                                           // K blocks issued so far, over all items
+            WorkItem wi;
+            bool ok = true;
+            while (ok && sched.next(wi)) {
+                int tm, tn;
+                pair_tile_coords(wi.tile, tiles_m, tiles_n, tm, tn);
+                const int m0 = tm * 256 + (int)rank * BM, nb0 = tn * BN + (int)rank * HALF_N;
+                const int kb_end = min(wi.c1 * CHUNK_KB, nkb);
+                for (int kb = wi.c0 * CHUNK_KB; kb < kb_end; kb++, it++) {
+                    const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, status, 1)) { ok = false; break; }
+                    const uint32_t st = smem0 + s * STAGE_BYTES;
+                    const uint32_t full_leader = map_to_cta(full0 + 8 * s, 0);
+                    if (leader) mbar_expect_tx(full0 + 8 * s, 2 * STAGE_BYTES);
+                    tma_load_2d_pair(st, &map_a_hi, full_leader, kb * BK, m0);
+                    tma_load_2d_pair(st + A_BYTES, &map_a_lo, full_leader, kb * BK, m0);
+                    tma_load_2d_pair(st + 2 * A_BYTES, &map_b_hi, full_leader, kb * BK, nb0);
+                    tma_load_2d_pair(st + 2 * A_BYTES + B_BYTES, &map_b_lo, full_leader, kb * BK, nb0);
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        // ---- MMA issuer: one lane of the leader CTA issues for the pair ----
+        if (leader && lane == 0) {
+            constexpr uint32_t idesc = instr_desc_pair(BN);
+            uint32_t it = 0, g = 0;                                    // K blocks and chunks consumed so far
+            WorkItem wi;
+            bool ok = true;
+            while (ok && sched.next(wi)) {
+                for (int ch = wi.c0; ch < wi.c1 && ok; ch++, g++) {
+                    const uint32_t buf = g & 1u;
+                    ok = mbar_wait(acc_empty0 + 8 * buf, ((g >> 1) & 1u) ^ 1u, status, 4);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t tacc = tmem + buf * (uint32_t)BN;
+                    const int kb_end = min((ch + 1) * CHUNK_KB, nkb);
+                    bool first = true;
+                    for (int kb = ch * CHUNK_KB; kb < kb_end; kb++, it++) {
+                        const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
+                        ok = mbar_wait(full0 + 8 * s, ph, status, 2);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint32_t st = smem0 + s * STAGE_BYTES;
+                        const uint64_t a_hi = smem_desc(st), a_lo = smem_desc(st + A_BYTES);
+                        const uint64_t b_hi = smem_desc(st + 2 * A_BYTES), b_lo = smem_desc(st + 2 * A_BYTES + B_BYTES);
+#pragma unroll
+                        for (int k = 0; k < BK / UMMA_K; k++) {
+                            const uint64_t adv = (uint64_t)((k * UMMA_K * 4) >> 4);
+                            umma_tf32_pair(tacc, a_lo + adv, b_hi + adv, idesc, first ? 0u : 1u);
+                            umma_tf32_pair(tacc, a_hi + adv, b_lo + adv, idesc, 1u);
+                            umma_tf32_pair(tacc, a_hi + adv, b_hi + adv, idesc, 1u);
+                            first = false;
+                        }
+                        umma_commit_pair(empty0 + 8 * s);          // frees the stage in both CTAs
+                    }
+                    if (ok) umma_commit_pair(acc_full0 + 8 * buf);     // each CTA's half of the chunk is complete
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp >= 4) {
+        // ---- running sum + epilogue on this CTA's 128 rows ----
+        const int e = warp - 4, q = warp & 3, h = e >> 2;
+        const uint32_t acc_empty_leader0 = map_to_cta(acc_empty0, 0);
+        float acc[HALF];
+        uint32_t g = 0;
+        WorkItem wi;
+        bool ok = true;
+        while (ok && sched.next(wi)) {
+#pragma unroll
+            for (int j = 0; j < HALF; j++) acc[j] = 0.0f;
+            for (int ch = wi.c0; ch < wi.c1; ch++, g++) {
+                const uint32_t buf = g & 1u;
+                ok = __all_sync(0xffffffffu, ok && mbar_wait(acc_full0 + 8 * buf, (g >> 1) & 1u, status, 3));
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tsrc = tmem + ((uint32_t)(q * 32) << 16) + buf * (uint32_t)BN + (uint32_t)(h * HALF);
+#pragma unroll
+                for (int cc = 0; cc < HALF / 16; cc++) {
+                    uint32_t r[16];
+                    tmem_ld16(tsrc + (uint32_t)(cc * 16), r);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int j = 0; j < 16; j++) acc[cc * 16 + j] = __fadd_rn(acc[cc * 16 + j], __uint_as_float(r[j]));
+                }
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(acc_empty_leader0 + 8 * buf);    // the leader counts both CTAs
+            }
+            if (!ok) break;
+            int tm, tn;
+            pair_tile_coords(wi.tile, tiles_m, tiles_n, tm, tn);
+            const int row = tm * 256 + (int)rank * BM + q * 32 + lane, col0 = tn * BN + h * HALF;
+            const size_t slot = (size_t)(rank * 8 + e) * 128 * 32 + lane;
+            if (wi.c0 != 0) {
+                // not this tile's owner: hand the partial sums over (column-major per warp: coalesced)
+                float *dst = partial_ws + (size_t)cl * PARTIAL_FLOATS + slot;
+#pragma unroll
+                for (int j = 0; j < HALF; j++) dst[j * 32] = acc[j];
+                __threadfence();
+                __syncwarp();
+                if (lane == 0) atomicAdd(flags + cl, 1u);
+            } else {
+                if (wi.c1 != sched.nck) {
+                    // owner of a shared tile: add the partials of the clusters that hold the rest of its K, in order
+                    const long long tile_end = (long long)(wi.tile - sched.nfull * C + 1) * sched.nck;
+                    for (int j = cl + 1; j < C && ok; j++) {
+                        const long long bj = sched.tail_begin(j);
+                        if (bj >= tile_end) break;
+                        if (sched.tail_begin(j + 1) == bj) continue;                 // that cluster has no work
+                        bool got = lane == 0 ? flag_wait(flags + j, 16u, status, 5) : true;
+                        ok = __all_sync(0xffffffffu, got);
+                        if (!ok) break;
+                        const float *src = partial_ws + (size_t)j * PARTIAL_FLOATS + slot;
+#pragma unroll
+                        for (int jj = 0; jj < HALF; jj++) acc[jj] = __fadd_rn(acc[jj], __ldcg(src + jj * 32));
+                    }
+                    if (!ok) break;
+                }
+                if (*(volatile int *)status_word != 0) { ok = false; break; }
+                store_row<HALF>(c, acc, row, col0, M, N);
+            }
+        }
+        if (!__all_sync(0xffffffffu, ok)) {
+            // A wait ran out: give copies that may still be in flight time to land
+            // before the shared memory is released.
+            for (int i = 0; i < 64; i++) __nanosleep(4000);
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();     // nobody frees or exits while the peer may still signal or read
+    if (warp == 1)
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
 }

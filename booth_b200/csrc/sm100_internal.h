@@ -51,6 +51,7 @@ typedef struct sm100_api {
                              unsigned, unsigned, unsigned, unsigned, CUstream,
                              void **, void **);
     CUresult (*LaunchKernelEx)(const CUlaunchConfig *, CUfunction, void **, void **);   /* optional */
+    CUresult (*OccupancyMaxActiveClusters)(int *, CUfunction, const CUlaunchConfig *);  /* optional */
     CUresult (*GetErrorString)(CUresult, const char **);
     CUresult (*TensorMapEncodeTiled)(CUtensorMap *, CUtensorMapDataType, cuuint32_t,
                                      void *, const cuuint64_t *, const cuuint64_t *,
@@ -73,7 +74,7 @@ enum {
     SM100_K_REDUCE_I32, SM100_K_REDUCE_F32,
     SM100_K_ASIAN_MC, SM100_K_ASIAN_MC_PRECISE,
     SM100_K_ASIAN_PATHS, SM100_K_ASIAN_PATHS_PRECISE,
-    SM100_K_GEMM_PREPASS, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128,
+    SM100_K_GEMM_PREPASS, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_PERSIST,
     SM100_K_COUNT
 };
 
@@ -106,6 +107,7 @@ struct sm100_dev {
     int         gemm_pending;          /* a GEMM was enqueued since the last status check */
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
     unsigned    gemm_wait_ms;          /* limit of the GEMM kernel's barrier waits */
+    int         gemm_clusters;         /* CTA pairs of the persistent GEMM kernel this GPU holds at once (0 = not asked yet) */
     /* The GEMM's four tensor maps (64-byte aligned, allocated on first use) and what they were encoded for. */
     CUtensorMap *gemm_maps;
     struct { CUdeviceptr ws; int Mp, Np, Kp, box_b, valid; } gemm_maps_key;

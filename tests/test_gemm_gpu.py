@@ -130,13 +130,58 @@ def test_gemm_full_size_sampled_rows(sm, dev, oracle_lib, M, size):
         dev.free(p)
 
 
+@pytest.mark.parametrize("clusters,shapes", [
+    ("5", [(512, 768, 4096), (1024, 1024, 2048)]),     # one tail tile shared by five clusters; a tail too short to divide
+    ("3", [(512, 1024, 8192), (768, 512, 1024)]),      # two tail tiles over three clusters: partial first, then owner
+    ("7", [(768, 1280, 4096)]),                        # two full waves and one shared tile
+])
+def test_persistent_form_with_few_clusters(sm, clusters, shapes):
+    """The persistent contraction's scheduling paths at sizes a test can afford: with
+    the number of clusters held down (BOOTH_SM100_GEMM_CLUSTERS) a few hundred rows
+    already make several waves and a tail whose K chunks are dealt out over clusters,
+    including tiles shared by more than two of them and clusters that first hand a
+    partial sum over and then own the next tile. Checked against a float64 product,
+    against the one-tile-per-cluster form (same tolerance), and for repeatability."""
+    code = r"""
+import os, sys, numpy as np, booth_b200 as sm
+shapes = %r
+d = sm.Device(0)
+for (M, N, K) in shapes:
+    a = sm.fill_host(M * K, 31, 0, 0).reshape(M, K); b = sm.fill_host(K * N, 31, 1, 0).reshape(K, N)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    da, db, dc = d.upload(a), d.upload(b), d.alloc(M * N * 4)
+    outs = []
+    for persist in ("1", "1", "0"):
+        os.environ["BOOTH_SM100_GEMM_PERSIST"] = persist
+        d.zero(dc, M * N * 4)
+        d.gemm(dc, da, db, M, N, K); d.sync()
+        outs.append(d.download(dc, (M, N), np.float32))
+    rel = [float(np.linalg.norm(o.astype(np.float64) - ref) / np.linalg.norm(ref)) for o in outs]
+    print((M, N, K), "rel", ["%%.2e" %% r for r in rel], "ok", all(r <= 1e-5 for r in rel),
+          "repeatable", bool(np.array_equal(outs[0], outs[1])),
+          "forms agree", float(np.abs(outs[0] - outs[2]).max()) <= 1e-5 * float(np.abs(ref).max()))
+    for p in (da, db, dc): d.free(p)
+d.close()
+""" % (shapes,)
+    import subprocess, sys
+    from conftest import ROOT
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                         text=True, timeout=300, env=dict(os.environ, BOOTH_SM100_GEMM_CLUSTERS=clusters))
+    assert res.returncode == 0, res.stdout + res.stderr
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("(")]
+    assert len(lines) == len(shapes)
+    for ln in lines:
+        assert "ok True repeatable True forms agree True" in ln, ln
+
+
 @pytest.mark.parametrize("pair", ["1", "0"])
 def test_barrier_wait_limit_reports_instead_of_hanging(sm, pair):
     """Failure detection without a fault: with the TMA producer kept silent (a
     host-side flag of the call) nothing ever signals the "operands ready" barrier, so the MMA
     issuer's and the epilogue's bounded waits run out (limit 50 ms here), the
     kernel records which wait gave up, frees its tensor memory and returns; the
-    host reads the status at the next sync. The device stays usable."""
+    host reads the status at the next call that waits. The device stays usable.
+    512 x 512 rows run the persistent pair form (pair = "1") or the one-CTA form."""
     code = r"""
 import os, numpy as np, booth_b200 as sm
 d = sm.Device(0)
