@@ -148,7 +148,7 @@ static const char *const k_names[SM100_K_COUNT] = {
     "reduce_sum_i32", "reduce_sum_f32",
     "asian_mc", "asian_mc_precise",
     "asian_paths", "asian_paths_precise",
-    "gemm_prepass", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta", "gemm_tf32x3_2cta_n128", "gemm_tf32x3_persist",
+    "gemm_prepass", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta", "gemm_tf32x3_2cta_n128", "gemm_tf32x3_persist", "gemm_tf32x3_fused",
 };
 
 int sm100_rt_device_count(void)
@@ -581,6 +581,10 @@ CUdeviceptr sm100_gemm_ws(sm100_dev_t *dev, size_t bytes)
     if (dev->gemm_ws) { a->MemFree(dev->gemm_ws); dev->gemm_ws = 0; dev->gemm_ws_bytes = 0; }
     CUresult cr = a->MemAlloc(&dev->gemm_ws, bytes);
     if (cr != CUDA_SUCCESS) { sm100_fail(dev, "GEMM workspace alloc", cr); dev->gemm_ws = 0; return 0; }
+    /* A fresh workspace starts as zeros: the persistent GEMM compares words in it with a
+     * per-call tag that is never zero. */
+    cr = a->MemsetD8Async(dev->gemm_ws, 0, bytes, dev->stream);
+    if (cr != CUDA_SUCCESS) { sm100_fail(dev, "clearing the GEMM workspace", cr); a->MemFree(dev->gemm_ws); dev->gemm_ws = 0; return 0; }
     dev->gemm_ws_bytes = bytes;
     return dev->gemm_ws;
 }
