@@ -824,121 +824,12 @@ constexpr int PARTIAL_FLOATS = 2 * 8 * 128 * 32;     // one cluster's slot: [cta
 
 }  // namespace gemm
 
-namespace gemm {
-
-// What the fused form's converter warps need to know.
-struct SplitJob {
-    const float *a, *b;                 // the caller's fp32 operands
-    float *a_hi, *a_lo, *b_hi, *b_lo;   // the planes in the workspace
-    unsigned *ready;                    // one word per (K chunk, 128-row block of A or of B^T)
-    unsigned epoch;                     // this call's tag; a word equal to it means "converted"
-    int M, N, Kraw, Mp, keep_b;         // Kraw: the unpadded K (the planes' row length is the padded K)
-};
-
-__device__ __forceinline__ void bar_sync_converters() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
-
-__device__ __forceinline__ void split4(const float4 v, float4 &h, float4 &l)
-{
-    h.x = to_tf32(v.x); l.x = to_tf32(v.x - h.x);
-    h.y = to_tf32(v.y); l.y = to_tf32(v.y - h.y);
-    h.z = to_tf32(v.z); l.z = to_tf32(v.z - h.z);
-    h.w = to_tf32(v.w); l.w = to_tf32(v.w - h.w);
-}
-
-// One item of A: rows [r0, r0+128) x K values [k0, k0+128) of the planes (row length Kp),
-// from A[M, K] row-major, zeros beyond M and K. t = 0..127, one row's 512 bytes per warp
-// and step, eight 16-byte loads in flight per thread.
-__device__ __forceinline__ void convert_a_item(const SplitJob &j, int Kp, int r0, int k0, int t)
-{
-    const bool vec = (j.Kraw & 3) == 0 && (((uintptr_t)j.a) & 15) == 0;
-    const int kw = min(128, Kp - k0) >> 2;                       // float4 per row of this item (Kp % 32 == 0)
-#pragma unroll 1
-    for (int base = 0; base < 128 * 32; base += 128 * 8) {
-        float4 v[8];
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int idx = base + u * 128 + t, row = r0 + (idx >> 5), c4 = idx & 31, k = k0 + 4 * c4;
-            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (c4 < kw && row < j.M) {
-                const float *src = j.a + (long long)row * j.Kraw + k;
-                if (vec && k + 3 < j.Kraw) v[u] = __ldcs(reinterpret_cast<const float4 *>(src));
-                else {
-                    if (k + 0 < j.Kraw) v[u].x = src[0];
-                    if (k + 1 < j.Kraw) v[u].y = src[1];
-                    if (k + 2 < j.Kraw) v[u].z = src[2];
-                    if (k + 3 < j.Kraw) v[u].w = src[3];
-                }
-            }
-        }
-#pragma unroll
-        for (int u = 0; u < 8; u++) {
-            const int idx = base + u * 128 + t, row = r0 + (idx >> 5), c4 = idx & 31;
-            if (c4 >= kw) continue;
-            float4 h, l;
-            split4(v[u], h, l);
-            const long long o = (long long)row * Kp + k0 + 4 * c4;
-            *reinterpret_cast<float4 *>(j.a_hi + o) = h;
-            *reinterpret_cast<float4 *>(j.a_lo + o) = l;
-        }
-    }
-}
-
-// One item of B: rows [n0, n0+128) of B^T x K values [k0, k0+128), from B[K, N]
-// row-major, as four 64 x 64 tiles transposed through shared memory by the 128
-// converter threads (16-byte loads along n, 16-byte stores along k).
-__device__ __forceinline__ void convert_b_item(const SplitJob &j, int Kp, int n0, int k0, int t, float (*tile)[65])
-{
-    const int tx = t & 15, ty = t >> 4;                          // 16 x 8
-    const bool vec = (j.N & 3) == 0 && (((uintptr_t)j.b) & 15) == 0;
-#pragma unroll 1
-    for (int sub = 0; sub < 4; sub++) {
-        const int nn = n0 + (sub & 1) * 64, kk = k0 + (sub >> 1) * 64;
-        if (kk >= Kp) continue;                                  // uniform over the converter threads
-        float4 v[8];
-#pragma unroll
-        for (int p = 0; p < 8; p++) {
-            const int k = kk + ty + 8 * p, n = nn + 4 * tx;
-            v[p] = make_float4(0.f, 0.f, 0.f, 0.f);
-            if (k < j.Kraw) {
-                const float *src = j.b + (long long)k * j.N + n;
-                if (vec && n + 3 < j.N) v[p] = __ldcs(reinterpret_cast<const float4 *>(src));
-                else {
-                    if (n + 0 < j.N) v[p].x = src[0];
-                    if (n + 1 < j.N) v[p].y = src[1];
-                    if (n + 2 < j.N) v[p].z = src[2];
-                    if (n + 3 < j.N) v[p].w = src[3];
-                }
-            }
-        }
-        bar_sync_converters();                                   // the previous tile has been read
-#pragma unroll
-        for (int p = 0; p < 8; p++) {
-            float *d = &tile[ty + 8 * p][4 * tx];
-            d[0] = v[p].x; d[1] = v[p].y; d[2] = v[p].z; d[3] = v[p].w;
-        }
-        bar_sync_converters();
-#pragma unroll
-        for (int p = 0; p < 8; p++) {
-            const int nl = ty + 8 * p, k = kk + 4 * tx;          // one row of B^T, four consecutive k
-            if (k >= Kp) continue;
-            float4 h, l;
-            split4(make_float4(tile[4 * tx + 0][nl], tile[4 * tx + 1][nl], tile[4 * tx + 2][nl], tile[4 * tx + 3][nl]), h, l);
-            const long long o = (long long)(nn + nl) * Kp + k;
-            *reinterpret_cast<float4 *>(j.b_hi + o) = h;
-            *reinterpret_cast<float4 *>(j.b_lo + o) = l;
-        }
-    }
-}
-
-}  // namespace gemm
-
-template <bool FUSED>
-__device__ __forceinline__ void gemm_persist_body(const CUtensorMap &map_a_hi, const CUtensorMap &map_a_lo,
-                                                  const CUtensorMap &map_b_hi, const CUtensorMap &map_b_lo,
-                                                  float *__restrict__ c, int M, int N, int Np, int K, int tail_split,
-                                                  int *status_word, unsigned long long wait_ns, int silent_producer,
-                                                  float *__restrict__ partial_ws, unsigned *__restrict__ flags, unsigned epoch,
-                                                  const gemm::SplitJob &job)
+extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
+gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
+                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
+                    float *__restrict__ c, int M, int N, int Np, int K, int tail_split,
+                    int *status_word, unsigned long long wait_ns, int silent_producer,
+                    float *__restrict__ partial_ws, unsigned *__restrict__ flags, unsigned epoch)
 {
     using namespace gemm;
     constexpr int BN = 256, STAGES = 3, HALF_N = BN / 2, HALF = BN / 2, CHUNK_KB = 4;
@@ -950,7 +841,6 @@ __device__ __forceinline__ void gemm_persist_body(const CUtensorMap &map_a_hi, c
     extern __shared__ uint8_t smem_persist[];
     __shared__ __align__(8) uint64_t bars[2 * STAGES + 4];
     __shared__ uint32_t s_tmem;
-    __shared__ float conv_tile[FUSED ? 64 : 1][65];       // the converters' transpose tile
 
     const uint32_t rank = cluster_ctarank();
     const bool leader = rank == 0;
@@ -980,34 +870,11 @@ __device__ __forceinline__ void gemm_persist_body(const CUtensorMap &map_a_hi, c
     const uint32_t tmem = s_tmem;
     asm volatile("griddepcontrol.wait;" ::: "memory");       // the planes, the flags and C are touched only from here on
     asm volatile("griddepcontrol.launch_dependents;");
-    // Registers follow the roles (512 threads start with 128 each in the fused form, 384
-    // with 168 otherwise): the control warpgroup and the converters give up what they do not
-    // need, the two epilogue warpgroups (128 running sums per thread) take it. Each
-    // warpgroup changes its share as the first thing inside its own branch.
-    const int rb_a = job.Mp >> 7, rb_all = rb_a + (Np >> 7);          // 128-row blocks of A, then of B^T, per K chunk
-
-    if (FUSED && warp >= 12) {
-        asm volatile("setmaxnreg.dec.sync.aligned.u32 88;");
-        // ---- operand split, fused: the 128 converter threads of every CTA share the items
-        // (K chunk, 128-row block), K chunk by K chunk in the order the contraction consumes
-        // them, and publish each with a release store of this call's tag ----
-        const int t = (int)threadIdx.x - 384;
-        const int per_chunk = job.keep_b ? rb_a : rb_all;
-        const long long total = (long long)nck * per_chunk;
-        for (long long i = blockIdx.x; i < total; i += gridDim.x) {
-            const int ch = (int)(i / per_chunk), idx = (int)(i - (long long)ch * per_chunk);
-            if (idx < rb_a) convert_a_item(job, K, idx * 128, ch * (CHUNK_KB * BK), t);
-            else convert_b_item(job, K, (idx - rb_a) * 128, ch * (CHUNK_KB * BK), t, conv_tile);
-            __threadfence();
-            bar_sync_converters();
-            if (t == 0) {
-                asm volatile("fence.proxy.async;" ::: "memory");       // generic-proxy stores, read next by TMA
-                asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(job.ready + (long long)ch * rb_all + idx), "r"(job.epoch) : "memory");
-            }
-        }
-    } else if (warp < 4) {
-      if (FUSED) asm volatile("setmaxnreg.dec.sync.aligned.u32 48;");
-      else asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    // Registers follow the roles (384 threads start with 168 each): the control warpgroup
+    // gives up what it does not need, the two epilogue warpgroups (128 running sums per
+    // thread) take it. Each warpgroup changes its share as the first thing in its branch.
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
       if (warp == 0) {
         // ---- TMA producer, one lane in each CTA; completions count on the leader's barrier ----
         if (lane == 0 && !silent_producer) {
@@ -1020,13 +887,6 @@ __device__ __forceinline__ void gemm_persist_body(const CUtensorMap &map_a_hi, c
                 const int m0 = tm * 256 + (int)rank * BM, nb0 = tn * BN + (int)rank * HALF_N;
                 const int kb_end = min(wi.c1 * CHUNK_KB, nkb);
                 for (int kb = wi.c0 * CHUNK_KB; kb < kb_end; kb++, it++) {
-                    if (FUSED && (kb % CHUNK_KB == 0)) {
-                        // this CTA's rows of both operands for this K chunk must have been converted
-                        const unsigned *fa = job.ready + (long long)(kb / CHUNK_KB) * rb_all + (m0 >> 7);
-                        const unsigned *fb = job.ready + (long long)(kb / CHUNK_KB) * rb_all + rb_a + (nb0 >> 7);
-                        if (!flag_wait_eq(fa, job.epoch, status, 6) || (!job.keep_b && !flag_wait_eq(fb, job.epoch, status, 6))) { ok = false; break; }
-                        asm volatile("fence.proxy.async;" ::: "memory");
-                    }
                     const uint32_t s = it % STAGES, ph = (it / STAGES) & 1u;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, status, 1)) { ok = false; break; }
                     const uint32_t st = smem0 + s * STAGE_BYTES;
@@ -1081,8 +941,7 @@ __device__ __forceinline__ void gemm_persist_body(const CUtensorMap &map_a_hi, c
         __syncwarp();
       }
     } else if (warp < 12) {
-        if (FUSED) asm volatile("setmaxnreg.inc.sync.aligned.u32 184;");
-        else asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 208;");
         // ---- running sum + epilogue on this CTA's 128 rows ----
         const int e = warp - 4, q = warp & 3, h = e >> 2;
         const uint32_t acc_empty_leader0 = map_to_cta(acc_empty0, 0);
@@ -1159,37 +1018,4 @@ __device__ __forceinline__ void gemm_persist_body(const CUtensorMap &map_a_hi, c
     cluster_sync_all();     // nobody frees or exits while the peer may still signal or read
     if (warp == 1)
         asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
-}
-
-extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(384, 1)
-gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                    const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                    float *__restrict__ c, int M, int N, int Np, int K, int tail_split,
-                    int *status_word, unsigned long long wait_ns, int silent_producer,
-                    float *__restrict__ partial_ws, unsigned *__restrict__ flags, unsigned epoch)
-{
-    gemm::SplitJob none = {};
-    gemm_persist_body<false>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, tail_split, status_word, wait_ns,
-                             silent_producer, partial_ws, flags, epoch, none);
-}
-
-// The persistent form with the operand split inside: 512 threads, warps 12-15 of
-// every CTA convert A and B into the hi/lo planes while the other warps contract
-// what has been converted already, so the split costs no time of its own and no
-// launch (and the contraction's first reads of the planes hit L2). The TMA producer
-// waits for the two "converted" words of its rows and K chunk before it loads them.
-// The grid never exceeds the CTA pairs the GPU holds at once: converters of every
-// CTA run from the start, none of them waits for anything.
-extern "C" __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(512, 1)
-gemm_tf32x3_fused(const __grid_constant__ CUtensorMap map_a_hi, const __grid_constant__ CUtensorMap map_a_lo,
-                  const __grid_constant__ CUtensorMap map_b_hi, const __grid_constant__ CUtensorMap map_b_lo,
-                  float *__restrict__ c, int M, int N, int Np, int K, int tail_split,
-                  int *status_word, unsigned long long wait_ns, int silent_producer,
-                  float *__restrict__ partial_ws, unsigned *__restrict__ flags, unsigned epoch,
-                  const float *__restrict__ a, const float *__restrict__ b, float *a_hi, float *a_lo, float *b_hi, float *b_lo,
-                  unsigned *ready, int Kraw, int Mp, int keep_b)
-{
-    const gemm::SplitJob job = { a, b, a_hi, a_lo, b_hi, b_lo, ready, epoch, M, N, Kraw, Mp, keep_b };
-    gemm_persist_body<true>(map_a_hi, map_a_lo, map_b_hi, map_b_lo, c, M, N, Np, K, tail_split, status_word, wait_ns,
-                            silent_producer, partial_ws, flags, epoch, job);
 }

@@ -74,7 +74,7 @@ enum {
     SM100_K_REDUCE_I32, SM100_K_REDUCE_F32,
     SM100_K_ASIAN_MC, SM100_K_ASIAN_MC_PRECISE,
     SM100_K_ASIAN_PATHS, SM100_K_ASIAN_PATHS_PRECISE,
-    SM100_K_GEMM_PREPASS, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_PERSIST, SM100_K_GEMM_FUSED,
+    SM100_K_GEMM_PREPASS, SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA, SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_PERSIST,
     SM100_K_COUNT
 };
 
@@ -108,7 +108,6 @@ struct sm100_dev {
     int         gemm_smem_set;         /* dynamic shared memory limit raised on the GEMM kernels */
     unsigned    gemm_wait_ms;          /* limit of the GEMM kernel's barrier waits */
     unsigned    gemm_epoch;            /* tag of the latest persistent GEMM call (never zero once used) */
-    size_t      gemm_hdr_bytes;        /* size of the tagged-words header at the start of the GEMM workspace */
     int         gemm_clusters;         /* CTA pairs of the persistent GEMM kernel this GPU holds at once (0 = not asked yet) */
     /* The GEMM's four tensor maps (64-byte aligned, allocated on first use) and what they were encoded for. */
     CUtensorMap *gemm_maps;

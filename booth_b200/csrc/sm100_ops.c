@@ -548,24 +548,21 @@ static int gemm_cluster_capacity(sm100_dev_t *dev)
     if (dev->gemm_clusters > 0) return dev->gemm_clusters;
     int n = dev->sm_count / 2;
     if (dev->api->OccupancyMaxActiveClusters) {
-        static const struct { int which; unsigned threads; } forms[2] = { { SM100_K_GEMM_PERSIST, 384 }, { SM100_K_GEMM_FUSED, 512 } };
-        for (int f = 0; f < 2; f++) {
-            CUlaunchAttribute attr;
-            memset(&attr, 0, sizeof attr);
-            attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
-            attr.value.clusterDim.x = 2; attr.value.clusterDim.y = 1; attr.value.clusterDim.z = 1;
-            CUlaunchConfig cfg;
-            memset(&cfg, 0, sizeof cfg);
-            cfg.gridDimX = (unsigned)(dev->sm_count & ~1); cfg.gridDimY = 1; cfg.gridDimZ = 1;
-            cfg.blockDimX = forms[f].threads; cfg.blockDimY = 1; cfg.blockDimZ = 1;
-            cfg.sharedMemBytes = 197632;
-            cfg.hStream = dev->stream;
-            cfg.attrs = &attr; cfg.numAttrs = 1;
-            /* the kernel's dynamic shared memory limit must be raised before the question makes sense */
-            if (dev->api->FuncSetAttribute(dev->k[forms[f].which], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, 197632) != CUDA_SUCCESS)
-                continue;
+        CUlaunchAttribute attr;
+        memset(&attr, 0, sizeof attr);
+        attr.id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        attr.value.clusterDim.x = 2; attr.value.clusterDim.y = 1; attr.value.clusterDim.z = 1;
+        CUlaunchConfig cfg;
+        memset(&cfg, 0, sizeof cfg);
+        cfg.gridDimX = (unsigned)(dev->sm_count & ~1); cfg.gridDimY = 1; cfg.gridDimZ = 1;
+        cfg.blockDimX = 384; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = 197632;
+        cfg.hStream = dev->stream;
+        cfg.attrs = &attr; cfg.numAttrs = 1;
+        /* the kernel's dynamic shared memory limit must be raised before the question makes sense */
+        if (dev->api->FuncSetAttribute(dev->k[SM100_K_GEMM_PERSIST], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, 197632) == CUDA_SUCCESS) {
             int got = 0;
-            if (dev->api->OccupancyMaxActiveClusters(&got, dev->k[forms[f].which], &cfg) == CUDA_SUCCESS && got > 0 && got < n)
+            if (dev->api->OccupancyMaxActiveClusters(&got, dev->k[SM100_K_GEMM_PERSIST], &cfg) == CUDA_SUCCESS && got > 0 && got < n)
                 n = got;
         }
     }
@@ -598,48 +595,30 @@ int booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_pt
     const size_t a_bytes = (size_t)Mp * Kp * 4, b_bytes = (size_t)Np * Kp * 4, planes = 2 * a_bytes + 2 * b_bytes;
     /* The persistent form (one cluster per SM pair walks a list of tiles, the tail's K
      * chunks dealt out evenly) serves the 256 x 256 pair tiles; BOOTH_SM100_GEMM_PERSIST=0
-     * falls back to one tile per cluster. By default it also splits the operands itself
-     * (BOOTH_SM100_GEMM_FUSED=0: a separate launch does). Workspace of the persistent form:
-     *   [ header: "converted" words of the fused split, one per (K chunk, 128-row block),
-     *             then 16 hand-over words per cluster ]  a fixed place, so that words left
-     *             by earlier calls keep their older tags whatever the shapes were
+     * falls back to one tile per cluster. Its workspace:
+     *   [ 16 KiB header: 16 hand-over words per cluster, compared with a per-call tag,
+     *     so nothing is cleared between calls (a fresh workspace is zeros, a tag never is) ]
      *   [ planes A_hi, A_lo, Bt_hi, Bt_lo ]
      *   [ one 256 KiB slot of partial sums per cluster ]
-     * The header's words are compared with a per-call tag: nothing is cleared between calls. */
+     * (the other forms leave the header alone and use the planes only). */
     const int persist = pair && bn == 256 && env_int("BOOTH_SM100_GEMM_PERSIST", 1, 0, 1);
-    const int fused = persist && env_int("BOOTH_SM100_GEMM_FUSED", 1, 0, 1);
     int clusters = 0;
     if (persist && (clusters = gemm_cluster_capacity(dev)) < 1) return SM100_ERR_CUDA;
-    const int nck = (Kp / 32 + 3) / 4;
-    const size_t ready_bytes = (size_t)nck * (size_t)(Mp / 128 + Np / 128) * 4, handover_bytes = 256 * 16 * 4;
-    size_t hdr = 0;
-    if (persist) {
-        hdr = ((ready_bytes + 255) & ~(size_t)255) + handover_bytes;
-        if (hdr < ((size_t)1 << 20)) hdr = (size_t)1 << 20;
-        if (hdr < dev->gemm_hdr_bytes) hdr = dev->gemm_hdr_bytes;      /* never shrinks: the words keep their place */
-        if (hdr > dev->gemm_hdr_bytes && dev->gemm_ws) {
-            /* a larger header moves everything behind it: start from a fresh, zeroed workspace */
-            dev->api->StreamSynchronize(dev->stream);
-            dev->api->MemFree(dev->gemm_ws);
-            dev->gemm_ws = 0; dev->gemm_ws_bytes = 0; dev->gemm_b.valid = 0;
-        }
-        dev->gemm_hdr_bytes = hdr;
-    }
-    const size_t slot_bytes = (size_t)2 * 8 * 128 * 32 * 4;
-    CUdeviceptr ws = sm100_gemm_ws(dev, persist ? hdr + planes + (size_t)clusters * slot_bytes : planes);
+    const size_t hdr = 256 * 16 * 4, slot_bytes = (size_t)2 * 8 * 128 * 32 * 4;
+    CUdeviceptr ws = sm100_gemm_ws(dev, hdr + planes + (size_t)clusters * slot_bytes);
     if (!ws) return SM100_ERR_CUDA;
-    const CUdeviceptr base = ws + (persist ? dev->gemm_hdr_bytes : 0);
+    const CUdeviceptr base = ws + hdr;
     CUdeviceptr a_hi = base, a_lo = base + a_bytes, b_hi = base + 2 * a_bytes, b_lo = b_hi + b_bytes;
-    CUdeviceptr partial_ws = base + planes, ready_ptr = ws, flags_ptr = ws + dev->gemm_hdr_bytes - handover_bytes;
+    CUdeviceptr partial_ws = base + planes, flags_ptr = ws;
     CUtensorMap *maps = NULL;
     if ((rc = gemm_maps(dev, base, Mp, Np, Kp, pair ? bn / 2 : bn, &maps)) != SM100_OK) return rc;
 
     const unsigned shmem = 197632;     /* stages * stage bytes + 1024: 2 x 96 KB, 3 x 64 KB or 4 x 48 KB, the same for every form */
     if (!dev->gemm_smem_set) {
         CUresult cr = CUDA_SUCCESS;
-        static const int forms[6] = { SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA,
-                                      SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_PERSIST, SM100_K_GEMM_FUSED };
-        for (int i = 0; i < 6 && cr == CUDA_SUCCESS; i++)
+        static const int forms[5] = { SM100_K_GEMM_TF32X3, SM100_K_GEMM_TF32X3_N128, SM100_K_GEMM_TF32X3_2CTA,
+                                      SM100_K_GEMM_TF32X3_2CTA_N128, SM100_K_GEMM_PERSIST };
+        for (int i = 0; i < 5 && cr == CUDA_SUCCESS; i++)
             cr = dev->api->FuncSetAttribute(dev->k[forms[i]], CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, (int)shmem);
         if (cr != CUDA_SUCCESS) return sm100_fail(dev, "raising the GEMM kernel's shared memory limit", cr);
         dev->gemm_smem_set = 1;
@@ -654,7 +633,7 @@ int booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_pt
     if (persist) {
         /* The tail (tiles % clusters) is dealt out by K chunks of 128 when that leaves every
          * cluster at least four chunks and a real share of the pairs would otherwise idle. */
-        const int rem = tiles % clusters;
+        const int rem = tiles % clusters, nck = (Kp / 32 + 3) / 4;
         tail_split = rem > 0 && rem <= clusters - clusters / 8 && (long long)rem * nck / clusters >= 4 &&
                      env_int("BOOTH_SM100_GEMM_SPLIT_TAIL", 1, 0, 1);
         launch_clusters = tail_split || tiles >= clusters ? clusters : tiles;
@@ -669,23 +648,21 @@ int booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_pt
 
     /* 1. One launch ahead of the contraction: split A, split + transpose B (both write
      * zeros into the padding) and zero the tiles of C that clusters of the one-tile form
-     * share; the fused persistent form does all of this itself and needs no such launch. A is split one 16-byte chunk per thread
+     * share. A is split one 16-byte chunk per thread
      * (measured 6.0 / 6.7 TB/s at 4096^2 / 8192^2 against 5.2 / 5.7 for eight persistent
      * blocks per SM), B in 64 x 64 tiles. The planes of B can stay from the previous call
      * when the caller says B has not changed and they are still where that call put them. */
     const int keep_b = (flags & BOOTH_GEMM_B_UNCHANGED) && dev->gemm_b.valid && dev->gemm_b.b == b &&
                        dev->gemm_b.planes == b_hi && dev->gemm_b.K == K && dev->gemm_b.N == N;
     if (!keep_b) dev->gemm_b.valid = 0;
-    if (!fused) {
-        long long a_chunks = (long long)Mp * (Kp / 4), a_blocks = (a_chunks + 255) / 256;
-        long long b_blocks = keep_b ? 0 : (long long)(Np / 64) * ((Kp + 63) / 64);
-        if (a_blocks + b_blocks + shared > 0x7fffffffll) a_blocks = 0x7fffffffll - b_blocks - shared;
-        if (a_blocks < 1) return bad_arg(dev, "booth_sm100_gemm: operands too large for one launch");
-        unsigned ua = (unsigned)a_blocks, ub = (unsigned)b_blocks;
-        int tiles_n = Np / 256;
-        void *pa[] = { &a, &a_hi, &a_lo, &M, &K, &Mp, &Kp, &b, &b_hi, &b_lo, &N, &Np, &c, &tiles_n, &split_from, &ua, &ub };
-        if ((rc = sm100_launch_k_overlapped(dev, SM100_K_GEMM_PREPASS, ua + ub + (unsigned)shared, 256, 0, pa)) != SM100_OK) return rc;
-    }
+    long long a_chunks = (long long)Mp * (Kp / 4), a_blocks = (a_chunks + 255) / 256;
+    long long b_blocks = keep_b ? 0 : (long long)(Np / 64) * ((Kp + 63) / 64);
+    if (a_blocks + b_blocks + shared > 0x7fffffffll) a_blocks = 0x7fffffffll - b_blocks - shared;
+    if (a_blocks < 1) return bad_arg(dev, "booth_sm100_gemm: operands too large for one launch");
+    unsigned ua = (unsigned)a_blocks, ub = (unsigned)b_blocks;
+    int tiles_n = Np / 256;
+    void *pa[] = { &a, &a_hi, &a_lo, &M, &K, &Mp, &Kp, &b, &b_hi, &b_lo, &N, &Np, &c, &tiles_n, &split_from, &ua, &ub };
+    if ((rc = sm100_launch_k_overlapped(dev, SM100_K_GEMM_PREPASS, ua + ub + (unsigned)shared, 256, 0, pa)) != SM100_OK) return rc;
 
     /* 2. The tiled contraction. Barrier waits inside the kernel give up after
      * gemm_wait_ms (booth_sm100_gemm_wait_limit; 4 s unless set). With
@@ -696,12 +673,9 @@ int booth_sm100_gemm_ex(sm100_dev_t *dev, sm100_ptr_t c, sm100_ptr_t a, sm100_pt
     if (persist) {
         if (++dev->gemm_epoch == 0) dev->gemm_epoch = 1;            /* this call's tag; zero is what a fresh workspace holds */
         unsigned epoch = dev->gemm_epoch;
-        int keep = keep_b;
         void *gp[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &M, &N, &Np, &Kp, &tail_split, &status, &wait_ns, &silent,
-                       &partial_ws, &flags_ptr, &epoch, &a, &b, &a_hi, &a_lo, &b_hi, &b_lo, &ready_ptr, &K, &Mp, &keep };
-        /* the first sixteen parameters are the persistent kernel's; the fused one takes them all */
-        rc = fused ? sm100_launch_k3_overlapped(dev, SM100_K_GEMM_FUSED, 2u * (unsigned)launch_clusters, 1, 1, 512, 1, 1, shmem, gp)
-                   : sm100_launch_k3_overlapped(dev, SM100_K_GEMM_PERSIST, 2u * (unsigned)launch_clusters, 1, 1, 384, 1, 1, shmem, gp);
+                       &partial_ws, &flags_ptr, &epoch };
+        rc = sm100_launch_k3_overlapped(dev, SM100_K_GEMM_PERSIST, 2u * (unsigned)launch_clusters, 1, 1, 384, 1, 1, shmem, gp);
     } else {
         void *ga[] = { &maps[0], &maps[1], &maps[2], &maps[3], &c, &M, &N, &Np, &Kp, &split_from, &status, &wait_ns, &silent };
         if (pair)

@@ -148,7 +148,7 @@ static const char *const k_names[SM100_K_COUNT] = {
     "reduce_sum_i32", "reduce_sum_f32",
     "asian_mc", "asian_mc_precise",
     "asian_paths", "asian_paths_precise",
-    "gemm_prepass", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta", "gemm_tf32x3_2cta_n128", "gemm_tf32x3_persist", "gemm_tf32x3_fused",
+    "gemm_prepass", "gemm_tf32x3", "gemm_tf32x3_n128", "gemm_tf32x3_2cta", "gemm_tf32x3_2cta_n128", "gemm_tf32x3_persist",
 };
 
 int sm100_rt_device_count(void)

@@ -83,44 +83,40 @@ d.sync(); d.close()
                        ("reduce_sum_f32", (1, 1, 1), 256), ("asian_mc", (4736, 1, 1), 256),
                        ("asian_mc_precise", (4, 1, 1), 256)]
     g = seq[5:]
-    # 4096^3: ONE launch does it all, the persistent contraction with the operand split inside: 74 clusters of
-    # two CTAs (one per SM pair), 512 threads, 197,632 bytes of dynamic shared memory, programmatic serialization
-    assert g[0] == ("gemm_tf32x3_fused", (148, 1, 1), 512)
-    assert L[5]["shmem"] == 197632 and L[5]["overlap"] == 1
-    # same B declared unchanged, then 8192^3 (other shape): the same single launch each
-    assert g[1:3] == [("gemm_tf32x3_fused", (148, 1, 1), 512)] * 2
-    # 100 x 200 x 50 pads to 128 x 256 x 64: the one-CTA form, one tile, behind the separate split launch
-    # (8 blocks split A, one 16-byte chunk per thread; 4 blocks split and transpose 64 x 64 tiles of B)
-    assert g[3:] == [("gemm_prepass", (8 + 4, 1, 1), 256), ("gemm_tf32x3", (1, 1, 1), 320)]
+    # 4096^3: ONE launch ahead of the contraction (16384 blocks split A, one 16-byte chunk per thread;
+    # 64 x 64 blocks split and transpose B), then the persistent contraction: 74 clusters of two CTAs (one per
+    # SM pair), 384 threads, 197,632 bytes of dynamic shared memory; both with programmatic stream serialization
+    assert g[:2] == [("gemm_prepass", (16384 + 4096, 1, 1), 256), ("gemm_tf32x3_persist", (148, 1, 1), 384)]
+    assert L[5 + 1]["shmem"] == 197632 and L[5]["overlap"] == 1 and L[5 + 1]["overlap"] == 1
+    # same B declared unchanged: no B blocks
+    assert g[2:4] == [("gemm_prepass", (16384, 1, 1), 256), ("gemm_tf32x3_persist", (148, 1, 1), 384)]
+    # 8192^3: B split again despite the flag (other shape)
+    assert g[4:6] == [("gemm_prepass", (65536 + 16384, 1, 1), 256), ("gemm_tf32x3_persist", (148, 1, 1), 384)]
+    # 100 x 200 x 50 pads to 128 x 256 x 64: the one-CTA form, one tile
+    assert g[6:] == [("gemm_prepass", (8 + 4, 1, 1), 256), ("gemm_tf32x3", (1, 1, 1), 320)]
     maps = [ln for ln in lines if ln.startswith("tensormap")]
     assert maps[-4:] == ["tensormap dims 64 128 stride 256 box 32 128"] * 2 + ["tensormap dims 64 256 stride 256 box 32 256"] * 2
     # the maps are encoded once per (workspace, padded shape): the two 4096^3 calls share theirs
     assert len(maps) == 3 * 4
 
 
-def test_gemm_forms_and_small_grids(fake, tmp_path):
-    """BOOTH_SM100_GEMM_FUSED=0 keeps the operand split in its own launch ahead of the
-    persistent contraction; BOOTH_SM100_GEMM_PERSIST=0 selects the one-tile-per-cluster
-    contraction (with its zeroed shared tiles); the persistent form launches no more
-    clusters than it has tiles when the tail is not divided."""
+def test_gemm_one_tile_per_cluster_form_and_small_grids(fake, tmp_path):
+    """BOOTH_SM100_GEMM_PERSIST=0 selects the one-tile-per-cluster contraction (with its
+    zeroed shared tiles); the persistent form launches no more clusters than it has
+    tiles when the tail is not divided."""
     res, L, _ = run(fake, tmp_path, """
 import os
 d = sm.Device(0); x = d.alloc(64); y = d.alloc(64); out = d.alloc(64)
 d.gemm(out, x, y, 512, 768, 512)                 # 6 pair tiles, K too short to divide: 6 clusters
 d.gemm(out, x, y, 512, 4096, 4096)               # 32 tiles on 74 pairs: the tail is dealt out by K chunks, all 74 clusters
-os.environ["BOOTH_SM100_GEMM_FUSED"] = "0"
-d.gemm(out, x, y, 4096, 4096, 4096)
-d.gemm(out, x, y, 4096, 4096, 4096, b_unchanged=True)
 os.environ["BOOTH_SM100_GEMM_PERSIST"] = "0"
 d.gemm(out, x, y, 4096, 4096, 4096)
 d.sync(); d.close()
 """)
     assert res.returncode == 0, res.stderr
     seq = [(l["kernel"], l["grid"], l["block"][0]) for l in L]
-    assert seq[:2] == [("gemm_tf32x3_fused", (12, 1, 1), 512), ("gemm_tf32x3_fused", (148, 1, 1), 512)]
-    assert seq[2:6] == [("gemm_prepass", (16384 + 4096, 1, 1), 256), ("gemm_tf32x3_persist", (148, 1, 1), 384),
-                        ("gemm_prepass", (16384, 1, 1), 256), ("gemm_tf32x3_persist", (148, 1, 1), 384)]
-    assert seq[6:] == [("gemm_prepass", (16384 + 4096 + 34, 1, 1), 256), ("gemm_tf32x3_2cta", (580, 1, 1), 320)]
+    assert seq[1] == ("gemm_tf32x3_persist", (12, 1, 1), 384) and seq[3] == ("gemm_tf32x3_persist", (148, 1, 1), 384)
+    assert seq[4:] == [("gemm_prepass", (16384 + 4096 + 34, 1, 1), 256), ("gemm_tf32x3_2cta", (580, 1, 1), 320)]
 
 
 def test_gemm_outcome_reaches_every_call_that_waits(fake, tmp_path):
