@@ -994,7 +994,9 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                         const long long bj = sched.tail_begin(j);
                         if (bj >= tile_end) break;
                         if (sched.tail_begin(j + 1) == bj) continue;                 // that cluster has no work
-                        bool got = lane == 0 ? flag_wait_eq(flags + j * 16 + (int)rank * 8 + e, epoch, status, 5) : true;
+                        // every lane does the acquire load itself (one broadcast access per warp), so each
+                        // lane's reads of the partial sums below are ordered after the writer's release
+                        const bool got = flag_wait_eq(flags + j * 16 + (int)rank * 8 + e, epoch, status, 5);
                         ok = __all_sync(0xffffffffu, got);
                         if (!ok) break;
                         const float *src = partial_ws + (size_t)j * PARTIAL_FLOATS + slot;

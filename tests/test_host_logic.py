@@ -147,6 +147,18 @@ d.close()
     assert res.stderr.count("gave up waiting on a barrier (code 3") == 4
 
 
+def test_gemm_wait_limit_arguments(fake, tmp_path):
+    res, _, _ = run(fake, tmp_path, """
+d = sm.Device(0)
+L = sm.lib()
+print("zero", L.booth_sm100_gemm_wait_limit(d.handle, 0), "huge", L.booth_sm100_gemm_wait_limit(d.handle, 60001),
+      "ok", L.booth_sm100_gemm_wait_limit(d.handle, 50), "null", L.booth_sm100_gemm_wait_limit(None, 50))
+d.close()
+""")
+    assert res.returncode == 0, res.stderr
+    assert "zero -7 huge -7 ok 0 null -7" in res.stdout
+
+
 def test_bad_result_addresses_are_refused_before_any_launch(fake, tmp_path):
     """A misaligned result address would fault on the device; the host refuses it."""
     res, L, _ = run(fake, tmp_path, """
