@@ -15,8 +15,14 @@
 // Two launches per GEMM:
 //   gemm_prepass    A[M,K]  -> A_hi, A_lo [Mp,Kp]          (elementwise, streaming)
 //                   B[K,N]  -> Bt_hi, Bt_lo [Np,Kp]        (split + transpose through
-//                   shared memory, so both MMA operands are K-major), and zeros in
-//                   the tiles of C that two clusters add into
+//                   shared memory, so both MMA operands are K-major), and, for the
+//                   one-tile-per-cluster pair form only, zeros in the tiles of C that
+//                   two clusters add into
+//   the contraction, in one of three forms: gemm_tf32x3 (below: one CTA per tile),
+//                   gemm_tf32x3_2cta (a CTA pair per 256 x 256 tile) and
+//                   gemm_tf32x3_persist (CTA pairs that stay and walk a list of
+//                   tiles; the host's choice for 256-row tiles). The roles are the
+//                   same in all three:
 //   gemm_tf32x3     one 128 x BN tile of C per CTA:
 //       warp 0, one lane : TMA producer. cp.async.bulk.tensor (128-byte swizzle, no
 //                          multicast) brings the four operand tiles of a 32-wide
