@@ -44,7 +44,7 @@ def test_inject_must_fail(sm):
 def test_full_size_cases(sm):
     res = run("--backends", "cpu,sm100", "--full")
     assert res.returncode == 0, res.stdout
-    assert "saxpy/n=268435456" in res.stdout and "gemm/k=8192,m=8192,n=8192,rows4=16" in res.stdout
+    assert "saxpy/n=268435456" in res.stdout and "gemm/k=8192,m=8192,n=8192,rows4=64" in res.stdout
 
 
 @pytest.mark.gpu
