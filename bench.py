@@ -532,7 +532,7 @@ def run_ours(args):
         # ---- fp32 GEMM (config 3): row blocks of A per GPU, B replicated ----
         sizes = [int(v) for v in args.gemm_sizes.split(",")]
         workloads.extend(run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc if not args.no_parity else None, check,
-                                  0 if args.no_e2e else Ke))
+                                  0 if args.no_e2e else Ke, args.gemm_shard_of))
 
     line = {
         "metric": "saxpy_hbm_gbs", "value": saxpy_gbs, "unit": "GB/s", "n_gpus": G, "steps": K, "warmup": W,
@@ -648,13 +648,14 @@ def run_e2e_saxpy(sm, dev, ranks, n, steps, placement):
             "launcher_api": launcher}
 
 
-def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps):
+def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps, shard_of=0):
     out = []
     G = ranks.world
     # 3xTF32: three TF32 MMAs per fp32 product; TF32 dense rate is half the bf16 rate.
     peak = peaks["bf16_tflops"] / 2.0 / 3.0
     for size in sizes:
-        M = size // G
+        # shard_of: on one GPU, time (and check) the row block one of `shard_of` GPUs would hold
+        M = size // (shard_of if shard_of and G == 1 else G)
         a, b, c = dev.alloc(M * size * 4), dev.alloc(size * size * 4), dev.alloc(M * size * 4)
         dev.fill(a, ranks.rank * M * size, M * size, SEED + 3, 0, sm.FILL_F32_PM1)
         dev.fill(b, 0, size * size, SEED + 3, 1, sm.FILL_F32_PM1)
@@ -665,15 +666,17 @@ def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps):
             for p in (a, b, c):
                 dev.free(p)
             continue
-        tf = 2.0 * size * size * size / (t * 1e-3) / 1e12
+        flop = 2.0 * M * G * size * size
+        tf = flop / (t * 1e-3) / 1e12
         # The same step with the caller stating that B has not changed since the last
         # call: the split, transposed copy of B in the workspace is reused. Reported
         # beside the full figure, never in its place.
         t_kept = timed(dev, ranks, W, K, lambda: dev.gemm(c, a, b, M, size, size, b_unchanged=True)) / K
-        traffic = NCU_TRAFFIC.get("gemm_%d" % size) if G == 1 else None
+        traffic = NCU_TRAFFIC.get("gemm_%d" % size) if G == 1 and not shard_of else None
         entry = {"name": "gemm_fp32_3xtf32_%d" % size, "metric": "tflops", "value": tf, "unit": "TFLOP/s",
-                 "ms_per_step": t, "sharding": "A/C row blocks of %d rows per GPU, B replicated" % M,
-                 "b_unchanged": {"value": 2.0 * size * size * size / (t_kept * 1e-3) / 1e12, "unit": "TFLOP/s",
+                 "ms_per_step": t, "sharding": "A/C row blocks of %d rows per GPU, B replicated" % M if not (shard_of and G == 1)
+                 else "the %d-row block one of %d GPUs holds, alone on this GPU" % (M, shard_of),
+                 "b_unchanged": {"value": flop / (t_kept * 1e-3) / 1e12, "unit": "TFLOP/s",
                                  "ms_per_step": t_kept,
                                  "note": "booth_sm100_gemm_ex(BOOTH_GEMM_B_UNCHANGED): B's planes kept from the previous call"},
                  "roofline": dict(roofline("tensor", tf / G, peak, "TFLOP/s", traffic, peaks),
@@ -714,7 +717,7 @@ def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps):
                 dev.d2h_async(hc_p, c, na)
                 dev.sync()
             dt_s, per_rank = wall(ranks, e2e_steps, host_step)
-            entry["e2e"] = {"value": 2.0 * size ** 3 * e2e_steps / dt_s / 1e12, "unit": "TFLOP/s", "steps": e2e_steps,
+            entry["e2e"] = {"value": flop * e2e_steps / dt_s / 1e12, "unit": "TFLOP/s", "steps": e2e_steps,
                             "h2d_bytes_per_step": (na + nb) * G, "d2h_bytes_per_step": na * G, "per_rank_s": per_rank,
                             "api": "sm100_rt_h2d_async(A, B) + booth_sm100_gemm + sm100_rt_d2h_async(C) + sm100_rt_sync"}
             for hp in (ha_p, hb_p, hc_p):
@@ -857,6 +860,8 @@ def main():
     ap.add_argument("--workloads", default="all",
                     help="comma list of the extra workloads to run: sweep,vadd,reduce,asian,gemm (default all)")
     ap.add_argument("--gemm-sizes", default=",".join(str(v) for v in GEMM_SIZES))
+    ap.add_argument("--gemm-shard-of", type=int, default=0,
+                    help="with one GPU: run the GEMM on the row block one of this many GPUs holds (M = size / this)")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-parity", action="store_true",
