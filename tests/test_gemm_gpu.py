@@ -76,7 +76,9 @@ def test_gemm_argument_errors(sm, dev):
 
 @pytest.mark.parametrize("M,N,K", [(1, 1, 1), (4, 4, 4), (100, 200, 50), (129, 257, 33), (128, 256, 30),
                                    (300, 1000, 514), (1000, 1000, 1000), (2500, 260, 64), (2100, 301, 99),
-                                   (2049, 515, 258), (768, 130, 4100)])
+                                   (2049, 515, 258), (768, 130, 4100),
+                                   # a tail dealt out by K chunks whose last chunk is short (K pads to 4128 = 32 chunks + 1 block)
+                                   (512, 4096, 4100)])
 def test_gemm_any_size(sm, dev, oracle_lib, M, N, K):
     """Sizes that are not whole tiles: the planes are zero-padded in the workspace
     and only the M x N that exist are stored (the memory after C stays untouched).

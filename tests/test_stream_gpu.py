@@ -248,3 +248,29 @@ def test_link_probe_reports_the_host_link(sm, dev):
     g = (C.c_double * 4)()
     assert sm.lib().booth_sm100_link_probe(dev.handle, 16, 1, g) == sm.ERR_ARG
     assert sm.lib().booth_sm100_link_probe(dev.handle, 1 << 20, 0, g) == sm.ERR_ARG
+
+
+def test_ieee_special_values_match_the_x86_64_path(sm, dev, oracle_lib):
+    """Signed zeros, infinities, subnormals, the largest finite values and products that
+    overflow or underflow: the unfused mul and add of the GPU kernels give the bits the
+    reference's x86-64 code (mulss, addss; no flush to zero on either side) gives. Where
+    the result is a NaN (inf - inf, 0 * inf) both sides must say NaN; the payload of a
+    NaN is the one thing the two machines are free to differ in, as the reference's own
+    comparison allows (tests/diff/bc_diff.h: two NaNs agree)."""
+    tiny, big = np.float32(1e-45), np.finfo(np.float32).max
+    pool = np.array([0.0, -0.0, 1.0, -1.0, np.inf, -np.inf, tiny, -tiny, 3e-39, -3e-39, 1.1754944e-38,
+                     big, -big, big / 2, 1.5e38, -1.5e38, 0.4, -0.4, 6e-39, 2.5], np.float32)
+    x = np.repeat(pool, pool.size)
+    y = np.tile(pool, pool.size)
+    n = x.size
+    dx, dy, dz = dev.upload(x), dev.upload(y), dev.alloc(n * 4)
+    dev.vadd(dx, dy, dz, n)
+    dev.saxpy(dy, dx, 2.5, n)
+    for got, want in ((dev.download(dz, n, np.float32), oracle_lib.vadd(x, y)),
+                      (dev.download(dy, n, np.float32), oracle_lib.saxpy(y, x, 2.5))):
+        nan = np.isnan(want)
+        assert np.array_equal(np.isnan(got), nan)
+        assert np.array_equal(got.view(np.uint32)[~nan], want.view(np.uint32)[~nan])
+        assert nan.any() and np.isinf(want).any() and (np.abs(want[~nan & (want != 0)]) < 1.2e-38).any()
+    for p in (dx, dy, dz):
+        dev.free(p)
