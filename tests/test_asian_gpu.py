@@ -92,3 +92,50 @@ def test_path_index_above_2_32(sm, dev, oracle_lib):
     s = gpu_sums(dev, prm, p0, 4096)
     oa, og = oracle_lib.asian(prm, p0, 4096)
     assert abs(s[0] - oa) <= 1e-4 * oa and abs(s[1] - og) <= 1e-4 * og
+
+
+@pytest.mark.parametrize("precise", [1, 0])
+@pytest.mark.parametrize("kw", [
+    dict(nstep=4), dict(nstep=12, sigma=0.8), dict(nstep=1000, sigma=0.05),            # few / many monitoring steps
+    dict(sigma=0.0),                                                                   # no noise: every path is the same
+    dict(strike=60.0), dict(strike=140.0, sigma=0.4),                                  # deep in and out of the money
+    dict(s0=0.5, strike=0.5, r=0.0), dict(s0=2.5e4, strike=2.4e4, r=0.11, T=3.0),      # other scales and horizons
+    dict(k0=7, k1=0xFFFFFFFF),                                                         # another key
+])
+def test_other_contracts_and_step_counts(sm, dev, oracle_lib, precise, kw):
+    """The benchmark prices one contract (S0 = K = 100, 252 steps); the kernel takes any.
+    Other step counts (any multiple of 4), volatilities down to zero, strikes far from the
+    money, other scales, rates, horizons and Philox keys against the CPU checker on the same
+    stream: both sums within 1e-5 relative (within 1e-7 of the notional where a payoff sum
+    is nearly zero)."""
+    npaths = 1 << 15
+    prm = sm.asian_params(precise=precise, **kw)
+    s = gpu_sums(dev, prm, 1000, npaths)
+    oa, og = oracle_lib.asian(prm, 1000, npaths)
+    floor = 1e-7 * npaths * float(prm.s0)
+    if kw.get("sigma") == 0.0 and not precise:
+        # Without noise every step multiplies the price by the same factor, and the CPU statement's
+        # fp32 chain s *= exp(x) then rounds the same way 252 times: its arithmetic price is 2.6e-4
+        # off the exact value (2.55302 against 2.552366 here). The MUFU flavour rebuilds the price from
+        # its running logarithm and does not share that drift, so it is held against the exact value
+        # (computed in double from the same fp32 drift), and the checker's own distance is recorded.
+        n, d = prm.nstep, float(prm.drift)
+        exact_a = npaths * (float(prm.s0) * sum(math.exp(d * j) for j in range(1, n + 1)) / n - float(prm.strike))
+        exact_g = npaths * (float(prm.s0) * math.exp(d * (n + 1) / 2.0) - float(prm.strike))
+        assert abs(s[0] - exact_a) <= REL * exact_a and abs(s[1] - exact_g) <= REL * exact_g
+        assert abs(oa - exact_a) > 10 * abs(s[0] - exact_a)
+        return
+    assert abs(s[0] - oa) <= max(REL * oa, floor), (kw, s[0] / npaths, oa / npaths)
+    assert abs(s[1] - og) <= max(REL * og, floor), (kw, s[1] / npaths, og / npaths)
+    assert oa >= og - floor                       # arithmetic mean >= geometric mean, also on the checker's side
+
+
+def test_step_counts_that_are_not_multiples_of_four_are_refused(sm, dev):
+    out = dev.alloc(32)
+    for nstep in (0, 1, 250, -4):
+        prm = sm.asian_params(nstep=max(nstep, 1))
+        prm.nstep = nstep
+        with pytest.raises(sm.Sm100Error) as e:
+            dev.asian(prm, 0, 16, out)
+        assert e.value.code == sm.ERR_ARG
+    dev.free(out)
