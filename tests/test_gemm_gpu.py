@@ -178,6 +178,44 @@ d.close()
         assert "ok True repeatable True forms agree True" in ln, ln
 
 
+@pytest.mark.parametrize("seed,clusters", [(11, ""), (12, "13"), (13, "3")])
+def test_random_shapes_against_a_double_precision_product(sm, seed, clusters):
+    """Seeded random shapes (rows that make one to twelve tile rows, ragged widths, K from
+    one block to several dozen chunks) through whatever contraction form the library picks,
+    with the GPU's own number of clusters and with it held down: relative Frobenius error
+    <= 1e-5 against a float64 product, and the call that keeps B's planes gives the same bits."""
+    code = r"""
+import os, numpy as np, booth_b200 as sm
+rng = np.random.default_rng(%d)
+d = sm.Device(0)
+for it in range(8):
+    M = int(rng.choice([256, 512, 768, 1024, 1280, 2048, 2304, 2500, 3000, 2049]))
+    N = int(rng.integers(1, 12)) * 256 - int(rng.choice([0, 0, 0, 1, 7, 100]))
+    K = int(rng.choice([32, 96, 128, 500, 512, 1000, 1024, 2048, 3000, 4096, 4100, 6144]))
+    a = rng.uniform(-1, 1, (M, K)).astype(np.float32); b = rng.uniform(-1, 1, (K, N)).astype(np.float32)
+    da, db, dc = d.upload(a), d.upload(b), d.alloc(M * N * 4)
+    d.gemm(dc, da, db, M, N, K); d.sync()
+    c = d.download(dc, (M, N), np.float32)
+    d.gemm(dc, da, db, M, N, K, b_unchanged=True); d.sync()
+    c2 = d.download(dc, (M, N), np.float32)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    rel = float(np.linalg.norm(c - ref) / np.linalg.norm(ref))
+    print("case", (M, N, K), "rel %%.2e" %% rel, "ok", rel <= 1e-5 and bool(np.array_equal(c, c2)))
+    for p in (da, db, dc): d.free(p)
+d.close()
+""" % seed
+    import subprocess, sys
+    from conftest import ROOT
+    env = dict(os.environ)
+    if clusters:
+        env["BOOTH_SM100_GEMM_CLUSTERS"] = clusters
+    res = subprocess.run([sys.executable, "-c", code], cwd=ROOT, stdout=subprocess.PIPE, stderr=subprocess.PIPE,
+                         text=True, timeout=600, env=env)
+    assert res.returncode == 0, res.stdout + res.stderr
+    lines = [ln for ln in res.stdout.splitlines() if ln.startswith("case")]
+    assert len(lines) == 8 and all(ln.endswith("ok True") for ln in lines), res.stdout
+
+
 @pytest.mark.parametrize("pair", ["1", "0"])
 def test_barrier_wait_limit_reports_instead_of_hanging(sm, pair):
     """Failure detection without a fault: with the TMA producer kept silent (a
