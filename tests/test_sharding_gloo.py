@@ -37,6 +37,24 @@ a, g = orc.asian(prm, ranks.rank * npaths, npaths)
 t = torch.tensor([a, g], dtype=torch.float64); dist.all_reduce(t)
 wa, wg = orc.asian(prm, 0, 2 * npaths)
 assert abs(float(t[0]) - wa) <= 1e-12 * wa and abs(float(t[1]) - wg) <= 1e-12 * wg
+# The benchmark's own parity plumbing, as bench.py uses it at N > 1: every rank sums its shard of
+# the global stream piece by piece with the checker's generator (no product code), the wrapped
+# int32 partial sums and the double partial sums travel through Ranks.sum, and the totals equal the
+# checker's sums of the whole stream generated in one go.
+m = 1 << 18
+first = ranks.rank * m
+acc_i, acc_f = 0, 0.0
+for off in range(0, m, 1 << 16):
+    acc_i = bench.wrap32(acc_i + orc.reduce_i32(orc.fill(1 << 16, 5, 0, 2, first=first + off)))
+    acc_f += orc.reduce_f32(orc.fill(1 << 16, 5, 1, 1, first=first + off))
+tot_i = bench.wrap32(int(ranks.sum([acc_i], integer=True)[0]))
+tot_f = ranks.sum([acc_f])[0]
+assert tot_i == orc.reduce_i32(orc.fill(2 * m, 5, 0, 2)), tot_i
+assert abs(tot_f - orc.reduce_f32(orc.fill(2 * m, 5, 1, 1))) <= 1e-12 * tot_f
+assert bench.wrap32(0x7FFFFFFF + 1) == -(1 << 31) and bench.wrap32(-(1 << 31) - 1) == 0x7FFFFFFF
+assert ranks.gather(1.5 + ranks.rank) == [1.5, 2.5]
+# the checker's generator and the library's give the same stream
+assert np.array_equal(orc.fill(1000, 99, 0, 2, first=lo), vi[:1000])
 # plumbing: max over ranks, byte broadcast, barrier
 assert ranks.max(10.0 + ranks.rank) == 11.0
 blob = ranks.bcast_bytes(bytes(range(128)) if ranks.rank == 0 else None)
