@@ -8,10 +8,9 @@
 // launch are flattened and walk the vectors in tiles of 256-bit accesses. A
 // launch far larger than any tuned one (one thread per element is eight times
 // more threads than 32-byte chunks) keeps only its first blocks working; the
-// others retire at once. The library launches saxpy under this name too;
-// vadd_stream is the vector add body without that test for the library's own
-// launches (with the test it needs more than the 48 registers the by-name kernels
-// are held to, see below, and spills).
+// others retire at once. saxpy_stream and vadd_stream are the same bodies for the
+// library's own, tuned launches, with twice the loads in flight per thread and the
+// registers that takes.
 //
 // Arithmetic matches the reference's x86-64 backend bit for bit: the product
 // and the sum of saxpy are rounded separately (mulss then addss,
@@ -30,7 +29,12 @@
 #include "common.cuh"
 
 // Threads per SM that an oversized launch of the by-name kernels keeps working.
+#ifndef STREAM_KEEP_LONG
 #define STREAM_KEEP_LONG 640      // vectors of 2^26 elements and more
+#endif
+#ifndef STREAM_BYNAME_REGS
+#define STREAM_BYNAME_REGS 32
+#endif
 #define STREAM_KEEP_SHORT 1536
 
 #define UNROLL 4      // 128-bit path: independent 16-byte loads per input per thread
@@ -73,16 +77,20 @@ __device__ __forceinline__ float4 axpy4(float a, float4 x, float4 y)
 // order, so when the launch has more than 128 blocks per SM the first `keep` (a
 // few per SM) start together and stream the whole vector
 // while the surplus blocks come and go beside them without touching memory; how
-// fast the SMs retire empty blocks (about 1.5 per ns) then sets the pace.
+// fast the GPU hands out and retires empty blocks (1.77 per ns for 256-thread blocks,
+// when nothing else occupies block slots) then sets the pace.
 template <bool SAXPY>
 __device__ __forceinline__ float op1(float a, float x, float y)
 {
     return SAXPY ? __fadd_rn(__fmul_rn(a, x), y) : __fadd_rn(x, y);
 }
 
-template <bool SAXPY, bool ANY_LAUNCH>
+template <bool SAXPY, bool ANY_LAUNCH, bool LEAN = false>
 __device__ __forceinline__ void stream_body(const float *x, const float *y, float *out, float a, long long n)
 {
+    // Loads in flight per thread and input: two 32-byte (four 16-byte) in the library's own
+    // launches; one (two) in the by-name kernels, which must live in 32 registers (see below).
+    constexpr int U8 = LEAN ? 1 : UNROLL8, U4 = LEAN ? 2 : UNROLL;
     const unsigned tid = flat_tid(), B = flat_bdim();
     const unsigned long long bid = flat_bid();
     unsigned long long G = flat_gdim();
@@ -115,18 +123,18 @@ __device__ __forceinline__ void stream_body(const float *x, const float *y, floa
         const f32x8 *x8 = reinterpret_cast<const f32x8 *>(x);
         const f32x8 *y8 = reinterpret_cast<const f32x8 *>(y);
         f32x8 *o8 = reinterpret_cast<f32x8 *>(out);
-        const long long tile = (long long)B * UNROLL8;
+        const long long tile = (long long)B * U8;
         const long long nfull = nvec / tile * tile;          // vectors covered by whole tiles
         // Branch-free main loop over whole tiles, so the loads of the next
         // iteration can be issued while this one's stores drain.
         for (long long base = (long long)bid * tile; base < nfull; base += (long long)G * tile) {
-            f32x8 xv[UNROLL8], yv[UNROLL8];
+            f32x8 xv[U8], yv[U8];
 #pragma unroll
-            for (int j = 0; j < UNROLL8; j++) xv[j] = ld256(x8 + base + (long long)j * B + tid);
+            for (int j = 0; j < U8; j++) xv[j] = ld256(x8 + base + (long long)j * B + tid);
 #pragma unroll
-            for (int j = 0; j < UNROLL8; j++) yv[j] = ld256(y8 + base + (long long)j * B + tid);
+            for (int j = 0; j < U8; j++) yv[j] = ld256(y8 + base + (long long)j * B + tid);
 #pragma unroll
-            for (int j = 0; j < UNROLL8; j++) {
+            for (int j = 0; j < U8; j++) {
                 f32x8 r;
 #pragma unroll
                 for (int e = 0; e < 8; e++) r.v[e] = op1<SAXPY>(a, xv[j].v[e], yv[j].v[e]);
@@ -146,19 +154,19 @@ __device__ __forceinline__ void stream_body(const float *x, const float *y, floa
         const float4 *x4 = reinterpret_cast<const float4 *>(x);
         const float4 *y4 = reinterpret_cast<const float4 *>(y);
         float4 *o4 = reinterpret_cast<float4 *>(out);
-        const long long tile = (long long)B * UNROLL;
+        const long long tile = (long long)B * U4;
         for (long long base = (long long)bid * tile; base < nvec; base += (long long)G * tile) {
             if (base + tile <= nvec) {
-                float4 xv[UNROLL], yv[UNROLL];
+                float4 xv[U4], yv[U4];
 #pragma unroll
-                for (int j = 0; j < UNROLL; j++) xv[j] = __ldcs(x4 + base + (long long)j * B + tid);
+                for (int j = 0; j < U4; j++) xv[j] = __ldcs(x4 + base + (long long)j * B + tid);
 #pragma unroll
-                for (int j = 0; j < UNROLL; j++) yv[j] = __ldcs(y4 + base + (long long)j * B + tid);
+                for (int j = 0; j < U4; j++) yv[j] = __ldcs(y4 + base + (long long)j * B + tid);
 #pragma unroll
-                for (int j = 0; j < UNROLL; j++)
+                for (int j = 0; j < U4; j++)
                     __stcs(o4 + base + (long long)j * B + tid, SAXPY ? axpy4(a, xv[j], yv[j]) : add4(xv[j], yv[j]));
             } else {
-                for (int j = 0; j < UNROLL; j++) {
+                for (int j = 0; j < U4; j++) {
                     const long long i = base + (long long)j * B + tid;
                     if (i < nvec) {
                         const float4 xv = __ldcs(x4 + i), yv = __ldcs(y4 + i);
@@ -178,15 +186,19 @@ __device__ __forceinline__ void stream_body(const float *x, const float *y, floa
 
 // out[i] = x[i] + y[i] for i < n_elements. block_size is the Triton BLOCK_SIZE
 // parameter of the reference kernel; the geometry comes from the launch itself.
-// The by-name kernels are held to 48 registers: under a one-thread-per-element
-// launch of 256-thread blocks that leaves room for five blocks per SM, two that
-// work and three slots through which the empty ones pass (4.3 TB/s against 3.5
-// with four).
-extern "C" __global__ void __maxnreg__(48) vector_add(const float *x, const float *y, float *out,
+// The by-name kernels are held to 32 registers (one 32-byte load per input in flight
+// per thread instead of two): under a one-thread-per-element launch of 256-thread
+// blocks that leaves room for eight blocks per SM, two or three that work and five
+// slots through which the empty ones pass, and the launch then runs at the pace at
+// which the GPU hands out blocks: 2^30 elements in 2.40 ms, 5.47 TB/s, where the same
+// launch with n = 0 (every block empty) takes 2.37 ms. With 48 registers (five blocks
+// per SM) it was 4.29 TB/s, with 40 (six) 4.83. Under a caller's moderate geometry
+// the lean body reaches 6.3 to 6.6 TB/s (the library's own kernels 6.9).
+extern "C" __global__ void __maxnreg__(STREAM_BYNAME_REGS) vector_add(const float *x, const float *y, float *out,
                                                       int n_elements, int block_size)
 {
     (void)block_size;
-    stream_body<false, true>(x, y, out, 0.0f, (long long)n_elements);
+    stream_body<false, true, true>(x, y, out, 0.0f, (long long)n_elements);
 }
 extern "C" __global__ void vadd_stream(const float *x, const float *y, float *out, int n_elements, int block_size)
 {
@@ -195,9 +207,17 @@ extern "C" __global__ void vadd_stream(const float *x, const float *y, float *ou
 }
 
 // y[i] = a*x[i] + y[i] for i < n, product and sum rounded separately.
-extern "C" __global__ void __maxnreg__(48) saxpy(float *y, const float *x, float a, int n)
+extern "C" __global__ void __maxnreg__(STREAM_BYNAME_REGS) saxpy(float *y, const float *x, float a, int n)
 {
-    stream_body<true, true>(x, y, y, a, (long long)n);
+    stream_body<true, true, true>(x, y, y, a, (long long)n);
+}
+// The same for the library's own launches: tuned geometry, two 32-byte loads per input
+// in flight. (Built with the geometry test and 48 registers like the by-name kernel
+// used to be: that code reaches 6.92 TB/s at three 128-thread blocks per SM, the body
+// without the test 5.8 at the same geometry; the optimum is that sharp.)
+extern "C" __global__ void __maxnreg__(48) saxpy_stream(float *y, const float *x, float a, int n)
+{
+    stream_body<true, true, false>(x, y, y, a, (long long)n);
 }
 
 // ---- seeded inputs -------------------------------------------------------

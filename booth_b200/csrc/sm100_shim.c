@@ -144,7 +144,7 @@ int sm100_enter(sm100_dev_t *dev)
 /* ---- init / shut ---- */
 
 static const char *const k_names[SM100_K_COUNT] = {
-    "vadd_stream", "saxpy", "fill_philox",
+    "vadd_stream", "saxpy_stream", "fill_philox",
     "reduce_sum_i32", "reduce_sum_f32",
     "asian_mc", "asian_mc_precise",
     "asian_paths", "asian_paths_precise",

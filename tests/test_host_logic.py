@@ -59,7 +59,7 @@ d.vadd(x, y, y, 1 << 28); d.vadd(x, y, y, (1 << 24) + 5); d.saxpy(y, x, 1.0, 0)
 d.sync(); d.close()
 """)
     assert res.returncode == 0, res.stderr
-    assert [l["kernel"] for l in L] == ["saxpy"] * 5 + ["vadd_stream"] * 2          # n = 0 launches nothing
+    assert [l["kernel"] for l in L] == ["saxpy_stream"] * 5 + ["vadd_stream"] * 2   # n = 0 launches nothing
     assert all(l["block"] == (128, 1, 1) and l["overlap"] == 1 and l["shmem"] == 0 for l in L)
     # three persistent blocks per SM from 2^28 elements on; below that one 256-chunk tile per block,
     # at most 128 blocks per SM
@@ -333,8 +333,8 @@ d.close()
     assert "y unchanged by the fake: True" in res.stdout          # nothing computes on the CPU
     ops = [" ".join(ln.split()[:2]) for ln in lines if not ln.startswith("tensormap")]
     big, rest = 64 << 20, ((4 << 20) + 3) * 4
-    assert ops == ["h2d %d" % big, "h2d %d" % big, "launch saxpy", "d2h %d" % big,
-                   "h2d %d" % rest, "h2d %d" % rest, "launch saxpy", "d2h %d" % rest,
+    assert ops == ["h2d %d" % big, "h2d %d" % big, "launch saxpy_stream", "d2h %d" % big,
+                   "h2d %d" % rest, "h2d %d" % rest, "launch saxpy_stream", "d2h %d" % rest,
                    "h2d 4000", "h2d 4000", "launch vadd_stream", "d2h 4000"]
     assert [l["grid"][0] for l in L] == [8192, 2048, 1]
 
