@@ -455,19 +455,33 @@ static void tile_matmul(const char *what, float *a, float *b, float *c, int K, i
     }
     sm100_dev_t *d = host_dev(what);
     size_t na = span(4, sam, K, sak), nb = span(K, sbk, 4, sbn), nc = span(4, scm, 4, scn);
-    sm100_ptr_t da = sm100_rt_alloc(d, na * 4), db = sm100_rt_alloc(d, nb * 4), dc = sm100_rt_alloc(d, nc * 4);
-    if (!da || !db || !dc) host_die(what);
-    sm100_kern_t k;
-    if (sm100_rt_load_builtin(d, "matmul_tile", &k)) host_die(what);
+    /* Callers walk a matrix tile by tile with one call each (the reference's harnesses do),
+     * so the device buffers and the kernel handle are kept between calls: one allocation
+     * that only grows, cut into the three operands at 256-byte boundaries. */
+    static sm100_ptr_t buf;
+    static size_t buf_bytes;
+    static sm100_kern_t k;
+    const size_t oa = 0, ob = (na * 4 + 255) & ~(size_t)255, oc = ob + ((nb * 4 + 255) & ~(size_t)255);
+    const size_t need = oc + nc * 4;
+    pthread_mutex_lock(&g_host_mu);
+    if (need > buf_bytes) {
+        if (buf) sm100_rt_free(d, buf);
+        buf_bytes = need < (1u << 20) ? (1u << 20) : need * 2;
+        buf = sm100_rt_alloc(d, buf_bytes);
+        if (!buf) { buf_bytes = 0; pthread_mutex_unlock(&g_host_mu); host_die(what); }
+    }
+    if (!k.func && sm100_rt_load_builtin(d, "matmul_tile", &k)) { pthread_mutex_unlock(&g_host_mu); host_die(what); }
+    sm100_ptr_t da = buf + oa, db = buf + ob, dc = buf + oc;
     void *args[] = { &da, &db, &dc, &K, &block_k, &sam, &sak, &sbk, &sbn, &scm, &scn, &accumulate };
     /* The strided tile of c is written in place: bring the surrounding floats
-     * over first so the copy back leaves them untouched. */
-    if (sm100_rt_h2d(d, da, a, na * 4) || sm100_rt_h2d(d, db, b, nb * 4) ||
-        sm100_rt_h2d(d, dc, c, nc * 4) ||
-        sm100_rt_launch(d, &k, 1, 1, 1, 32, 1, 1, 0, args) ||
-        sm100_rt_d2h(d, c, dc, nc * 4))
-        host_die(what);
-    sm100_rt_free(d, da); sm100_rt_free(d, db); sm100_rt_free(d, dc);
+     * over first so the copy back leaves them untouched. The three uploads and the launch
+     * are queued on the device's stream; the copy back waits for them. */
+    int bad = sm100_rt_h2d_async(d, da, a, na * 4) || sm100_rt_h2d_async(d, db, b, nb * 4) ||
+              sm100_rt_h2d_async(d, dc, c, nc * 4) ||
+              sm100_rt_launch(d, &k, 1, 1, 1, 32, 1, 1, 0, args) ||
+              sm100_rt_d2h(d, c, dc, nc * 4);
+    pthread_mutex_unlock(&g_host_mu);
+    if (bad) host_die(what);
 }
 
 void matmul(float *a, float *b, float *c, int stride_am, int stride_ak, int stride_bk,

@@ -65,6 +65,28 @@ def test_tile_matmul_symbols_bit_exact_vs_golden(sm, dev):
     assert np.array_equal(C.view(np.uint32), GOLD["matmul_%dx%dx%d" % (M, N, K)])
 
 
+def test_tile_matmul_symbol_walks_a_matrix_like_the_reference_harness(sm, dev, oracle_lib):
+    """A caller of the CPU-launcher ABI multiplies matrices by calling matmul_k once per 4 x 4 tile
+    with offset base pointers. The library keeps its device buffers between such calls and regrows
+    them when a later call needs more (here: K = 64 first, then a 2 MiB-wide operand): every tile
+    bit-identical to the CPU checker's, memory around the strided C tile untouched."""
+    import time
+    L = sm.lib()
+    for M, N, K in ((16, 24, 64), (8, 8, 70000)):
+        A = sm.fill_host(M * K, SEED + 4, 0, 0).reshape(M, K); B = sm.fill_host(K * N, SEED + 4, 1, 0).reshape(K, N)
+        C = np.full((M, N + 4), -7.0, np.float32)            # four guard columns beside the result
+        t0 = time.perf_counter()
+        for mb in range(M // 4):
+            for nb in range(N // 4):
+                L.matmul_k(A[mb * 4:].ctypes.data, B[:, nb * 4:].ctypes.data, C[mb * 4:, nb * 4:].ctypes.data,
+                           K, K, 1, N, 1, N + 4, 1, 1)
+        per_call = (time.perf_counter() - t0) / ((M // 4) * (N // 4))
+        want = oracle_lib.matmul(A, B)
+        assert np.array_equal(C[:, :N].view(np.uint32), want.view(np.uint32)), (M, N, K)
+        assert np.all(C[:, N:] == np.float32(-7.0))
+        assert per_call < 0.05, per_call
+
+
 @pytest.mark.parametrize("precise", [1, 0])
 def test_asian_vs_golden(sm, dev, precise):
     prm = sm.asian_params(k0=SEED + 5, precise=precise)
