@@ -659,13 +659,17 @@ def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps, shard_of
         a, b, c = dev.alloc(M * size * 4), dev.alloc(size * size * 4), dev.alloc(M * size * 4)
         dev.fill(a, ranks.rank * M * size, M * size, SEED + 3, 0, sm.FILL_F32_PM1)
         dev.fill(b, 0, size * size, SEED + 3, 1, sm.FILL_F32_PM1)
+        gemm_sampler = ClockSampler(ranks.local)
+        gemm_sampler.start()
         try:
             t = timed(dev, ranks, W, K, lambda: dev.gemm(c, a, b, M, size, size)) / K
         except sm.Sm100Error as e:
+            gemm_sampler.stop()
             out.append({"name": "gemm_%d" % size, "unavailable": str(e)})
             for p in (a, b, c):
                 dev.free(p)
             continue
+        gemm_clocks = gemm_sampler.stop()
         flop = 2.0 * M * G * size * size
         tf = flop / (t * 1e-3) / 1e12
         # The same step with the caller stating that B has not changed since the last
@@ -685,7 +689,7 @@ def run_gemm(sm, dev, ranks, peaks, W, K, sizes, orc, check, e2e_steps, shard_of
                                                "hbm_bytes because it reads the split planes (2x) and re-reads panels: "
                                                "harmless, the kernel is bound by the tensor pipe" if traffic else
                                                "not captured for this shape"),
-                 "hbm_bytes": 4.0 * (M * size + size * size + M * size)}
+                 "hbm_bytes": 4.0 * (M * size + size * size + M * size), "clocks": gemm_clocks}
         if orc is not None:
             # 16 four-row blocks of this rank's rows of C against the CPU checker's 4x4x2 tiles
             # on the same seeded inputs (only the sampled rows of A are generated on the host)
