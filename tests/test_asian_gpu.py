@@ -139,3 +139,14 @@ def test_step_counts_that_are_not_multiples_of_four_are_refused(sm, dev):
             dev.asian(prm, 0, 16, out)
         assert e.value.code == sm.ERR_ARG
     dev.free(out)
+
+
+@pytest.mark.parametrize("precise", [1, 0])
+def test_same_bits_run_to_run(sm, dev, precise):
+    """No float atomics anywhere: per-thread double sums, a shuffle tree, and the block
+    that draws the last ticket adds the block partials in index order. Two runs of the
+    same launch give the same four doubles, bit for bit."""
+    prm = sm.asian_params(precise=precise)
+    first = gpu_sums(dev, prm, 12345, 300001)
+    for _ in range(3):
+        assert np.array_equal(gpu_sums(dev, prm, 12345, 300001).view(np.uint64), first.view(np.uint64))
