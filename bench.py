@@ -232,9 +232,9 @@ def timed_short(dev, ranks, warmup, steps, body, repeats=3):
 def mc_rooflines(path_steps_per_s, sm_count, clocks):
     """The pricer is bound by neither HBM nor the tensor pipe. Two issue limits
     apply per SM and clock: the special-function unit (3 MUFU operations per
-    path-step on 16 lanes: 16/3 path-steps) and the warp schedulers (20.8 warp
+    path-step on 16 lanes: 16/3 path-steps) and the warp schedulers (17.1 warp
     instructions per warp-step as counted by ncu, 4 schedulers x 32 lanes:
-    128/20.8 path-steps). Reported per GPU at the SM clock sampled during the
+    128/17.1 path-steps). Reported per GPU at the SM clock sampled during the
     timed region; the lower of the two ceilings is the `roofline`."""
     mhz = clocks.get("sm_mhz") or clocks.get("sm_max_mhz")
     clock_source = "sampled during the timed region"
@@ -244,10 +244,55 @@ def mc_rooflines(path_steps_per_s, sm_count, clocks):
     mufu = {"bound": "mufu issue", "achieved": achieved, "peak": 16.0 / 3.0, "unit": "path-steps/clk/SM",
             "frac": achieved / (16.0 / 3.0), "traffic": None, "sm_mhz": mhz, "sm_mhz_source": clock_source,
             "peak_source": "derived: 16 MUFU lanes per SM / 3 MUFU operations per path-step"}
-    issue = {"bound": "warp instruction issue", "achieved": achieved, "peak": 128.0 / 20.8, "unit": "path-steps/clk/SM",
-             "frac": achieved / (128.0 / 20.8),
-             "peak_source": "derived: 4 schedulers x 32 lanes / 20.8 warp instructions per warp-step (ncu, profiles/asian_mc_2p22.md)"}
+    issue = {"bound": "warp instruction issue", "achieved": achieved, "peak": 128.0 / 17.1, "unit": "path-steps/clk/SM",
+             "frac": achieved / (128.0 / 17.1),
+             "peak_source": "derived: 4 schedulers x 32 lanes / 17.1 warp instructions per warp-step (ncu, profiles/asian_mc_2p22.md)"}
     return mufu, issue
+
+
+def pipe_probe(sm, dev, mhz, achieved):
+    """Times the image's three probe kernels (kernels/pipe_probe.cu): the two
+    instruction groups the pricer cannot do without, per Philox call 12 MUFU and
+    20 IMAD.WIDE with their 20 xors, on independent register chains, alone and
+    together. A trip stands for four path-steps, so the pace of the two together
+    is a ceiling in the roofline's own unit (the pricer issues these and 16 more
+    instructions per call); `frac` is the pricer against it."""
+    import ctypes as C
+    L = sm.lib()
+    trips, blocks = 2048, dev.sm_count * 8
+    scratch = dev.alloc(64)
+    res = {"bound": "MUFU and IMAD.WIDE together (probe kernels, measured in this run)",
+           "unit": "path-steps/clk/SM", "trips": trips, "grid": [blocks, 256], "sm_mhz": mhz}
+    for name in ("probe_mufu", "probe_imad_wide", "probe_mufu_imad_wide"):
+        k = sm.Kern()
+        rc = L.sm100_rt_load_builtin(dev.handle, name.encode(), C.byref(k))
+        if rc != 0:
+            raise sm.Sm100Error("sm100_rt_load_builtin(%s)" % name, rc)
+        vals = [C.c_uint64(scratch), C.c_int(trips), C.c_float(0.999), C.c_uint32(12345)]
+        argv = (C.c_void_p * len(vals))(*[C.cast(C.byref(v), C.c_void_p) for v in vals])
+
+        def go():
+            rc = L.sm100_rt_launch(dev.handle, C.byref(k), blocks, 1, 1, 256, 1, 1, 0, argv)
+            if rc != 0:
+                raise sm.Sm100Error("sm100_rt_launch(%s)" % name, rc)
+        for _ in range(3):
+            go()
+        dev.sync()
+        dev.tic()
+        for _ in range(5):
+            go()
+        ms = dev.toc() / 5
+        # trips per warp scheduler (8 warps a block, 4 schedulers an SM) against the cycles the launch took
+        warp_trips = blocks * 8 * trips / (dev.sm_count * 4.0)
+        cyc = ms * 1e-3 * mhz * 1e6 / warp_trips
+        res[name] = {"ms": ms, "cycles_per_warp_trip_per_scheduler": cyc,
+                     "path_steps_per_clk_sm": 4 * 32 * 4.0 / cyc if cyc else None}
+        L.sm100_rt_unload(dev.handle, C.byref(k))
+    dev.free(scratch)
+    res["peak"] = res["probe_mufu_imad_wide"]["path_steps_per_clk_sm"]
+    res["achieved"] = achieved
+    res["frac"] = achieved / res["peak"] if res["peak"] else None
+    return res
 
 
 def roofline(bound, achieved, peak, unit, traffic, peaks):
@@ -505,6 +550,8 @@ def run_ours(args):
                      "price_arith": disc * s[0] / tot, "price_geom": disc * s[1] / tot,
                      "stderr_geom": disc * math.sqrt(max(s[3] / tot - (s[1] / tot) ** 2, 0.0) / tot),
                      "allreduce": bool(comm), "clocks": mc_clocks, "roofline": mufu, "second_bound": issue}
+            if not precise:
+                entry["pipe_probe"] = pipe_probe(sm, dev, mufu["sm_mhz"], mufu["achieved"])
             if not args.no_e2e:
                 # end to end: parameters in (a 32-byte struct by value), four doubles back
                 def mc_host_step():

@@ -6,9 +6,10 @@
 // Philox4x32-10 and a geometric-average payoff is priced beside the arithmetic
 // one. Everything a path needs lives in registers: the Philox state, the
 // running price, its logarithm and the two running sums. Nothing is read from
-// memory and only the reduced sums are written, so the kernel is bound by
-// instruction issue and by the special-function unit (ex2, lg2, sqrt, sin, cos:
-// three MUFU operations per path-step), not by HBM.
+// memory and only the reduced sums are written, so the kernel is bound by the
+// special-function unit (ex2, lg2, sqrt, sin, cos: three MUFU operations per
+// path-step) and by the generator's wide integer products on the heavy FMA pipe
+// (pipe_probe.cu times the two groups alone), not by HBM.
 //
 // Random stream, identical to the CPU statement of the workload:
 //   counter = (path low word, call index q, path high word, 0), key = (k0, k1);
@@ -25,20 +26,25 @@
 //            (src/ir/bir_lower.c:1757-1811): exp(x) = exp2(x*1.4426950f),
 //            log(x) = log2(x)*0.6931472f, sin/cos(x) = f(x*0.15915494f*6.2831855f);
 //   FAST     MUFU approximations (ex2/lg2/sqrt/sin/cos .approx), the step carried
-//            in base-2 logarithms (drift and vol pre-scaled by log2(e), one FMA
-//            forms the exponent) and the price rebuilt from its running logarithm,
-//            s_j = s0 * 2^(l_j), instead of a 252-long multiply chain.
+//            in base-2 logarithms (drift and vol pre-scaled by log2(e), vol folded
+//            into the Box-Muller radius so that one FMA forms the exponent), the
+//            floating-point work of a Philox call on the packed fp32x2 forms, and
+//            the price rebuilt from its running logarithm, s_j = s0 * 2^(l_j),
+//            instead of a 252-long multiply chain.
 // Payoffs are accumulated in double per thread, then warp shuffle -> shared ->
 // per-block partials -> the block that takes the last ticket adds them in index
 // order (no block waits for another).
 #include "common.cuh"
+
+// The 23 random bits as the mantissa of a float in [1, 2).
+__device__ __forceinline__ float mantissa_word(uint32_t x) { return __uint_as_float(0x3F800000u | (x >> 9)); }
 
 __device__ __forceinline__ float u01(uint32_t x)
 {
     // A shift and an OR, then one add. (One funnel shift, (0x7F : x) >> 9, gives the
     // same bits in one instruction less, but measured 2 % slower: 4.54e9 against
     // 4.62e9 paths/s.)
-    return __fadd_rn(__uint_as_float(0x3F800000u | (x >> 9)), -0.99999994f);
+    return __fadd_rn(mantissa_word(x), -0.99999994f);
 }
 
 __device__ __forceinline__ float mufu_ex2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
@@ -110,29 +116,46 @@ __device__ __forceinline__ Payoff asian_path(unsigned long long p, uint32_t k0, 
         // another, and, more important, the tiny negative bias of the MUFU ex2
         // (-3e-9 relative per evaluation, measured) is applied once per price instead
         // of compounding over 252 products (which moved the price by -8.4e-6).
-        // One FMA, three adds and one ex2 per step; mean(s) = s0 * mean(2^l_j).
-        const float d2 = drift * 1.4426950f, v2 = vol * 1.4426950f;
-        const float c_r = -2.0f * 0.6931472f;                          // -2 ln u = c_r * log2 u
-        float l = 0.0f, sum_e = 0.0f;
+        //
+        // vol is folded into the Box-Muller radius, vol*sqrt(-2 ln u) = sqrt((-2 ln2 vol^2) log2 u),
+        // so a step's exponent is one FMA (radius * cos + drift), and the angle is one FMA of
+        // the mantissa word. A Philox call yields two (cos, sin) pairs, i.e. four steps, and
+        // its floating-point work runs on the packed fp32x2 forms of sm_100 (two lanes per
+        // instruction): 11 instructions a call instead of 22 scalar ones. The running sums
+        // are kept as (even step, odd step) pairs and joined at the end. Besides the three
+        // MUFU operations of a step, the ten rounds of a call are 20 IMAD.WIDE on the heavy
+        // FMA pipe at a quarter of the FP32 rate; fewer FP32 instructions leave that pipe to
+        // them (4.79e9 against 4.60e9 paths per second). (vol below 1e-19, whose square
+        // underflows, prices like vol = 0.)
+        const float d2s = drift * 1.4426950f, v2 = vol * 1.4426950f;
+        const float c_rv = (-2.0f * 0.6931472f) * (v2 * v2);            // -2 ln u * v2^2 = c_rv * log2 u
+        const float2 c_rv2 = make_float2(c_rv, c_rv), d2 = make_float2(d2s, d2s);
+        const float2 two_pi = make_float2(6.2831855f, 6.2831855f);
+        const float2 ang0 = make_float2(-0.99999994f * 6.2831855f, -0.99999994f * 6.2831855f);
+        const float2 minus1 = make_float2(-0.99999994f, -0.99999994f);
+        float l = 0.0f;
+        float2 sum_e2 = make_float2(0.0f, 0.0f), sum_l2 = make_float2(0.0f, 0.0f);
         // Seven Philox calls per trip (252 steps are 9 trips) give the scheduler
         // independent chains; measured 4 % faster than two per trip.
 #pragma unroll 7
         for (int q = 0; q < ncall; q++) {
             const Philox4 r = philox4x32_10(plo, (uint32_t)q, phi, 0u, k0, k1);
-            const float u1 = u01(r.x), u2 = u01(r.y), u3 = u01(r.z), u4 = u01(r.w);
-            const float ra = mufu_sqrt(c_r * mufu_lg2(u1));
-            const float rb = mufu_sqrt(c_r * mufu_lg2(u3));
-            const float ta = 6.2831855f * u2, tb = 6.2831855f * u4;
-            float z[4];
-            z[0] = ra * mufu_cos(ta); z[1] = ra * mufu_sin(ta);
-            z[2] = rb * mufu_cos(tb); z[3] = rb * mufu_sin(tb);
-#pragma unroll
-            for (int i = 0; i < 4; i++) {
-                l += fmaf(v2, z[i], d2);
-                sum_e += mufu_ex2(l);
-                sum_l += l;
-            }
+            const float2 u13 = __fadd2_rn(make_float2(mantissa_word(r.x), mantissa_word(r.z)), minus1);
+            const float2 t = __ffma2_rn(make_float2(mantissa_word(r.y), mantissa_word(r.w)), two_pi, ang0);
+            const float2 rr = __fmul2_rn(c_rv2, make_float2(mufu_lg2(u13.x), mufu_lg2(u13.y)));
+            const float ra = mufu_sqrt(rr.x), rb = mufu_sqrt(rr.y);
+            const float2 xa = __ffma2_rn(make_float2(ra, ra), make_float2(mufu_cos(t.x), mufu_sin(t.x)), d2);
+            const float2 xb = __ffma2_rn(make_float2(rb, rb), make_float2(mufu_cos(t.y), mufu_sin(t.y)), d2);
+            const float2 la = __fadd2_rn(make_float2(l, l), make_float2(xa.x, xa.x + xa.y));
+            const float2 lb = __fadd2_rn(make_float2(la.y, la.y), make_float2(xb.x, xb.x + xb.y));
+            l = lb.y;
+            sum_e2 = __fadd2_rn(sum_e2, make_float2(mufu_ex2(la.x), mufu_ex2(la.y)));
+            sum_e2 = __fadd2_rn(sum_e2, make_float2(mufu_ex2(lb.x), mufu_ex2(lb.y)));
+            sum_l2 = __fadd2_rn(sum_l2, la);
+            sum_l2 = __fadd2_rn(sum_l2, lb);
         }
+        const float sum_e = sum_e2.x + sum_e2.y;
+        sum_l = sum_l2.x + sum_l2.y;
         const float inv_n = 1.0f / (float)nstep;
         const float am = s0 * (sum_e * inv_n) - strike;
         const float gm = s0 * exp2_fma(sum_l * inv_n) - strike;      // once per path: the accurate 2^x
@@ -196,9 +219,9 @@ __device__ __forceinline__ void asian_mc_body(double *out, unsigned long long pa
     if (threadIdx.x == 0) *ticket = 0u;
 }
 
-// The second launch bound frees the register budget: with 113 registers instead of
-// 64 the seven unrolled Philox calls of a trip really are independent chains (two
-// blocks per SM instead of four, 3.5 % more paths per second).
+// The second launch bound frees the register budget (116 registers, two blocks per
+// SM). The rate hardly depends on it: one to four blocks per SM and one to nine
+// Philox calls per trip all land within 3 % of one another.
 extern "C" __global__ void __launch_bounds__(256, 1)
 asian_mc(double *out, unsigned long long path0, unsigned long long npaths, uint32_t k0, uint32_t k1,
          float s0, float strike, float drift, float vol, int nstep, double *partials, unsigned *ticket)

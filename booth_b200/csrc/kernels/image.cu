@@ -6,6 +6,7 @@
 #include "asian.cu"
 #include "tile.cu"
 #include "canonical.cu"
+#include "pipe_probe.cu"
 #if __has_include("gemm_tf32x3.cu")
 #include "gemm_tf32x3.cu"
 #endif
