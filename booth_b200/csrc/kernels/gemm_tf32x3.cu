@@ -826,7 +826,7 @@ __device__ __forceinline__ bool flag_wait_eq(const unsigned *flag, unsigned tag,
     }
 }
 
-constexpr int PARTIAL_FLOATS = 2 * 8 * 128 * 32;     // one cluster's slot: [cta][epilogue warp][column][lane]
+constexpr int PARTIAL_FLOATS = 2 * 8 * 128 * 32;     // one cluster's slot: [cta][epilogue warp][4 columns][lane][4]
 
 }  // namespace gemm
 
@@ -980,12 +980,14 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
             int tm, tn;
             pair_tile_coords(wi.tile, tiles_m, tiles_n, tm, tn);
             const int row = tm * 256 + (int)rank * BM + q * 32 + lane, col0 = tn * BN + h * HALF;
-            const size_t slot = (size_t)(rank * 8 + e) * 128 * 32 + lane;
+            // a warp's slot holds [group of 4 columns][lane][4]: every access is 16 bytes a lane, 512 a warp
+            const size_t slot = (size_t)(rank * 8 + e) * 128 * 32;
             if (wi.c0 != 0) {
-                // not this tile's owner: hand the partial sums over (column-major per warp: coalesced)
-                float *dst = partial_ws + (size_t)cl * PARTIAL_FLOATS + slot;
+                // not this tile's owner: hand the partial sums over
+                float4 *dst = reinterpret_cast<float4 *>(partial_ws + (size_t)cl * PARTIAL_FLOATS + slot) + lane;
 #pragma unroll
-                for (int j = 0; j < HALF; j++) dst[j * 32] = acc[j];
+                for (int j = 0; j < HALF / 4; j++)
+                    dst[j * 32] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
                 __threadfence();
                 __syncwarp();
                 // one word per (cluster, CTA, epilogue warp), set to this call's tag: the owner's warp of
@@ -994,20 +996,29 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                     asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + cl * 16 + (int)rank * 8 + e), "r"(epoch) : "memory");
             } else {
                 if (wi.c1 != sched.nck) {
-                    // owner of a shared tile: add the partials of the clusters that hold the rest of its K, in order
+                    // owner of a shared tile: add the partials of the clusters that hold the rest of its K, always
+                    // from the last cluster down. The last one holds the tile's end as the first item of its own
+                    // list and has handed it over long ago; the ones between work on this tile to their very end,
+                    // so their sums arrive last and are waited for last.
                     const long long tile_end = (long long)(wi.tile - sched.nfull * C + 1) * sched.nck;
-                    for (int j = cl + 1; j < C && ok; j++) {
-                        const long long bj = sched.tail_begin(j);
-                        if (bj >= tile_end) break;
-                        if (sched.tail_begin(j + 1) == bj) continue;                 // that cluster has no work
+                    // the last cluster whose share begins before the tile's end: floor(j U / C) < end <=> j U < end C
+                    const int jlast = min(C - 1, (int)((tile_end * C - 1) / ((long long)sched.rem * sched.nck)));
+                    for (int j = jlast; j > cl && ok; j--) {
+                        if (sched.tail_begin(j + 1) == sched.tail_begin(j)) continue;   // that cluster has no work
                         // every lane does the acquire load itself (one broadcast access per warp), so each
                         // lane's reads of the partial sums below are ordered after the writer's release
                         const bool got = flag_wait_eq(flags + j * 16 + (int)rank * 8 + e, epoch, status, 5);
                         ok = __all_sync(0xffffffffu, got);
                         if (!ok) break;
-                        const float *src = partial_ws + (size_t)j * PARTIAL_FLOATS + slot;
+                        const float4 *src = reinterpret_cast<const float4 *>(partial_ws + (size_t)j * PARTIAL_FLOATS + slot) + lane;
 #pragma unroll
-                        for (int jj = 0; jj < HALF; jj++) acc[jj] = __fadd_rn(acc[jj], __ldcg(src + jj * 32));
+                        for (int jj = 0; jj < HALF / 4; jj++) {
+                            const float4 v = __ldcg(src + jj * 32);
+                            acc[4 * jj] = __fadd_rn(acc[4 * jj], v.x);
+                            acc[4 * jj + 1] = __fadd_rn(acc[4 * jj + 1], v.y);
+                            acc[4 * jj + 2] = __fadd_rn(acc[4 * jj + 2], v.z);
+                            acc[4 * jj + 3] = __fadd_rn(acc[4 * jj + 3], v.w);
+                        }
                     }
                     if (!ok) break;
                 }
