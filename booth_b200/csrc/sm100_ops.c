@@ -81,6 +81,8 @@ int booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y, sm100_ptr_t
     if (rc != SM100_OK) return rc;
     if (n < 0 || n > INT_MAX) return bad_arg(dev, "booth_sm100_vadd: n must be in [0, 2^31)");
     if (n == 0) return SM100_OK;
+    if (!x || !y || !out || ((x | y | out) & 3))
+        return bad_arg(dev, "booth_sm100_vadd: vectors must be non-NULL and 4-byte aligned");
     int ni = (int)n, bs = 256;
     const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &x, &y, &out, &ni, &bs };
@@ -93,6 +95,8 @@ int booth_sm100_saxpy(sm100_dev_t *dev, sm100_ptr_t y, sm100_ptr_t x, float a, l
     if (rc != SM100_OK) return rc;
     if (n < 0 || n > INT_MAX) return bad_arg(dev, "booth_sm100_saxpy: n must be in [0, 2^31)");
     if (n == 0) return SM100_OK;
+    if (!x || !y || ((x | y) & 3))
+        return bad_arg(dev, "booth_sm100_saxpy: vectors must be non-NULL and 4-byte aligned");
     int ni = (int)n;
     const unsigned block = (unsigned)env_int("BOOTH_SM100_STREAM_BLOCK", 128, 32, 1024);
     void *args[] = { &y, &x, &a, &ni };
@@ -144,10 +148,10 @@ int booth_sm100_asian(sm100_dev_t *dev, const booth_asian_t *p, long long path0,
     if (rc != SM100_OK) return rc;
     if (!p || !out || (out & 7) || npaths < 0 || path0 < 0 || p->nstep <= 0 || (p->nstep & 3))
         return bad_arg(dev, "booth_sm100_asian: bad argument (nstep must be a positive multiple of 4, out 8-byte aligned)");
-    /* 256-thread blocks, two resident per SM (113 registers). Thirty-two blocks per SM
+    /* 256-thread blocks, two resident per SM (116 registers). Thirty-two blocks per SM
      * in the grid, i.e. a hundred-odd paths per thread at 2^26 paths: the finer grain
-     * evens out the end of the launch (4.63e9 paths/s against 4.55e9 at 8 blocks per
-     * SM and 4.31e9 at 2; beyond 48 the per-block reduction starts to show). */
+     * evens out the end of the launch (1.5 % more paths per second than 8 blocks per
+     * SM, 7 % more than 2; beyond 48 the per-block reduction starts to show). */
     const unsigned block = 256;
     const int bpsm = env_int("BOOTH_SM100_ASIAN_BPSM", 32, 1, 128);
     long long g = (npaths + block - 1) / block;
@@ -255,17 +259,29 @@ static int stage_setup(sm100_dev_t *dev)
 {
     if (dev->stage_ready) return SM100_OK;
     const sm100_api_t *a = dev->api;
-    CUresult cr = a->StreamCreate(&dev->stream_out, CU_STREAM_NON_BLOCKING);
-    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "cuStreamCreate(copy-back stream)", cr);
-    cr = a->StreamCreate(&dev->stream_in, CU_STREAM_NON_BLOCKING);
-    if (cr != CUDA_SUCCESS) { a->StreamDestroy(dev->stream_out); return sm100_fail(dev, "cuStreamCreate(upload stream)", cr); }
-    for (int i = 0; i < SM100_STAGE_SLOTS && cr == CUDA_SUCCESS; i++) {
-        cr = a->EventCreate(&dev->ev_uploaded[i], CU_EVENT_DISABLE_TIMING);
-        if (cr == CUDA_SUCCESS) cr = a->EventCreate(&dev->ev_computed[i], CU_EVENT_DISABLE_TIMING);
-        if (cr == CUDA_SUCCESS) cr = a->EventCreate(&dev->ev_drained[i], CU_EVENT_DISABLE_TIMING);
+    CUstream s_out = NULL, s_in = NULL;
+    CUevent ev[3][SM100_STAGE_SLOTS];
+    CUdeviceptr stage = 0;
+    memset(ev, 0, sizeof ev);
+    CUresult cr = a->StreamCreate(&s_out, CU_STREAM_NON_BLOCKING);
+    if (cr == CUDA_SUCCESS) cr = a->StreamCreate(&s_in, CU_STREAM_NON_BLOCKING);
+    for (int k = 0; k < 3 && cr == CUDA_SUCCESS; k++)
+        for (int i = 0; i < SM100_STAGE_SLOTS && cr == CUDA_SUCCESS; i++)
+            cr = a->EventCreate(&ev[k][i], CU_EVENT_DISABLE_TIMING);
+    if (cr == CUDA_SUCCESS) cr = a->MemAlloc(&stage, (size_t)SM100_STAGE_SLOTS * 2 * SM100_STAGE_BYTES);
+    if (cr != CUDA_SUCCESS) {
+        /* nothing half-built is kept: the next call starts over */
+        for (int k = 0; k < 3; k++)
+            for (int i = 0; i < SM100_STAGE_SLOTS; i++)
+                if (ev[k][i]) a->EventDestroy(ev[k][i]);
+        if (s_in) a->StreamDestroy(s_in);
+        if (s_out) a->StreamDestroy(s_out);
+        return sm100_fail(dev, "setting up the staging ring (two streams, nine events, 384 MiB)", cr);
     }
-    if (cr == CUDA_SUCCESS) cr = a->MemAlloc(&dev->stage, (size_t)SM100_STAGE_SLOTS * 2 * SM100_STAGE_BYTES);
-    if (cr != CUDA_SUCCESS) return sm100_fail(dev, "setting up the staging ring", cr);
+    dev->stream_out = s_out; dev->stream_in = s_in; dev->stage = stage;
+    for (int i = 0; i < SM100_STAGE_SLOTS; i++) {
+        dev->ev_uploaded[i] = ev[0][i]; dev->ev_computed[i] = ev[1][i]; dev->ev_drained[i] = ev[2][i];
+    }
     dev->stage_ready = 1;
     return SM100_OK;
 }
@@ -281,7 +297,8 @@ static int stream_host(sm100_dev_t *dev, int saxpy, const float *x, const float 
 {
     int rc = sm100_enter(dev);
     if (rc != SM100_OK) return rc;
-    if (n < 0 || (n > 0 && (!x || !y || !out))) return bad_arg(dev, "booth_sm100_*_host: bad argument");
+    if (n < 0 || (n > 0 && (!x || !y || !out)) || (((uintptr_t)x | (uintptr_t)y | (uintptr_t)out) & 3))
+        return bad_arg(dev, "booth_sm100_*_host: bad argument (vectors non-NULL and 4-byte aligned)");
     if (n == 0) return SM100_OK;
     if ((rc = stage_setup(dev)) != SM100_OK) return rc;
     const sm100_api_t *api = dev->api;
@@ -408,6 +425,18 @@ static sm100_dev_t *host_dev(const char *what)
     return g_host_dev;
 }
 
+/* The reference's objects are plain functions that several host threads may call at
+ * once on disjoint ranges; here such calls share one device and one staging ring,
+ * so they take turns. */
+static void host_stream(const char *what, int is_saxpy, const float *x, const float *y, float *out, float a, long long m)
+{
+    sm100_dev_t *d = host_dev(what);
+    pthread_mutex_lock(&g_host_mu);
+    const int rc = stream_host(d, is_saxpy, x, y, out, a, m);
+    pthread_mutex_unlock(&g_host_mu);
+    if (rc != SM100_OK) host_die(what);
+}
+
 void vector_add(float *x, float *y, float *out, int n_elements, int block_size, int nthreads)
 {
     /* One call of the CPU launcher covers element indices [0, nthreads): the
@@ -415,8 +444,7 @@ void vector_add(float *x, float *y, float *out, int n_elements, int block_size, 
      * is not consulted. */
     (void)n_elements; (void)block_size;
     if (nthreads <= 0) return;
-    sm100_dev_t *d = host_dev("vector_add");
-    if (booth_sm100_vadd_host(d, x, y, out, nthreads) != SM100_OK) host_die("vector_add");
+    host_stream("vector_add", 0, x, y, out, 0.0f, nthreads);
 }
 
 void vadd(const float *a, const float *b, float *c, int n, int nthreads)
@@ -424,8 +452,7 @@ void vadd(const float *a, const float *b, float *c, int n, int nthreads)
     /* tests/ocaml/vadd_k.bir: c[i] = a[i] + b[i] for the threads with i < n. */
     long long m = nthreads < n ? nthreads : n;
     if (m <= 0) return;
-    sm100_dev_t *d = host_dev("vadd");
-    if (booth_sm100_vadd_host(d, a, b, c, m) != SM100_OK) host_die("vadd");
+    host_stream("vadd", 0, a, b, c, 0.0f, m);
 }
 
 void saxpy(float *y, float *x, float a, int n, int nthreads)
@@ -433,8 +460,7 @@ void saxpy(float *y, float *x, float a, int n, int nthreads)
     /* tests/canonical.cu:168-173: threads with idx >= n do nothing. */
     long long m = nthreads < n ? nthreads : n;
     if (m <= 0) return;
-    sm100_dev_t *d = host_dev("saxpy");
-    if (booth_sm100_saxpy_host(d, y, x, a, m) != SM100_OK) host_die("saxpy");
+    host_stream("saxpy", 1, x, y, y, a, m);
 }
 
 /* Extent, in floats, of a strided 4 x K (or K x 4) operand starting at its base. */

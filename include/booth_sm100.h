@@ -163,7 +163,10 @@ void booth_sm100_fill_host(void *dst, long long first, long long n,
  * the reference, whose pricer uses a counter hash (src/ocaml/Asian.ml:8-30). */
 void booth_sm100_philox4x32_10(const uint32_t ctr[4], const uint32_t key[2], uint32_t out[4]);
 
-/* out[i] = x[i] + y[i]: tests/tri_vadd.py:6-16, tests/vector_add.cu:4-10. */
+/* out[i] = x[i] + y[i]: tests/tri_vadd.py:6-16, tests/vector_add.cu:4-10.
+ * Vectors of this and the next call: device addresses, 4-byte aligned (any
+ * further alignment is found at run time), non-NULL when n > 0, n < 2^31; anything
+ * else returns SM100_ERR_ARG before any GPU work. */
 int  booth_sm100_vadd(sm100_dev_t *dev, sm100_ptr_t x, sm100_ptr_t y,
                       sm100_ptr_t out, long long n);
 /* y[i] = a*x[i] + y[i], product and sum rounded separately:
@@ -293,6 +296,8 @@ void sm100_comm_destroy(sm100_comm_t *comm);
  * kernel's own parameters followed by
  * nthreads (src/cpu/cpu_emit.c:386-431). They have no error channel; on failure
  * they print "sm100_rt: ..." and abort(), they never compute on the CPU.
+ * Like the reference's objects they may be called from several host threads at
+ * once (one range each); such calls share one device and take turns.
  * ------------------------------------------------------------------------- */
 void vector_add(float *x, float *y, float *out, int n_elements, int block_size,
                 int nthreads);

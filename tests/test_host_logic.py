@@ -170,12 +170,15 @@ print("f32 out+4", rc(d.reduce_f32, x, 100, out + 4), "i32 out+4", rc(d.reduce_i
       "i32 out+2", rc(d.reduce_i32, x, 100, out + 2), "null in", rc(d.reduce_f32, 0, 100, out),
       "null in n=0", rc(d.reduce_f32, 0, 0, out), "in+2", rc(d.reduce_i32, x + 2, 100, out),
       "asian out+4", rc(d.asian, sm.asian_params(), 0, 1000, out + 4))
+print("vadd x+2", rc(d.vadd, x + 2, x, x, 16), "vadd null out", rc(d.vadd, x, x, 0, 16), "saxpy y+1", rc(d.saxpy, x + 1, x, 2.0, 16),
+      "saxpy null x n=0", rc(d.saxpy, x, 0, 2.0, 0))
 print("noalloc out+4", sm.lib().booth_sm100_reduce_f32_noalloc(x, 100, out + 4, None),
       "noalloc null in", sm.lib().booth_sm100_reduce_f32_noalloc(0, 100, out, None))
 d.close()
 """)
     assert res.returncode == 0, res.stderr
     assert "f32 out+4 -7 i32 out+4 0 i32 out+2 -7 null in -7 null in n=0 0 in+2 -7 asian out+4 -7" in res.stdout
+    assert "vadd x+2 -7 vadd null out -7 saxpy y+1 -7 saxpy null x n=0 0" in res.stdout
     assert "noalloc out+4 -7 noalloc null in -7" in res.stdout
     assert [l["kernel"] for l in L] == ["reduce_sum_i32", "reduce_sum_f32"]     # only the two valid calls launched
 

@@ -109,6 +109,33 @@ def test_cpu_launcher_symbols_take_host_pointers(sm, dev, oracle_lib):
     assert mismatches(y, want) == 0
 
 
+def test_cpu_launcher_symbols_from_several_host_threads(sm, dev, oracle_lib):
+    """The reference's x86-64 kernels are plain functions, so a host may cut a vector
+    into ranges and call the symbol from one thread per range (offset pointers);
+    the library's symbols must stand that too. ctypes releases the GIL during a call."""
+    import threading
+    L = sm.lib()
+    T, per = 6, 1 << 20
+    n = T * per + 12345
+    x = sm.fill_host(n, 11, 0, 0); y = sm.fill_host(n, 11, 1, 0)
+    want_s = oracle_lib.saxpy(y, x, 2.5)
+    want_v = oracle_lib.vadd(x, y)
+    out = np.full(n, -1, np.float32)
+    bounds = [(t * per, (t + 1) * per if t < T - 1 else n) for t in range(T)]
+
+    def work(lo, hi):
+        L.vector_add(x.ctypes.data + 4 * lo, y.ctypes.data + 4 * lo, out.ctypes.data + 4 * lo, hi - lo, 256, hi - lo)
+    th = [threading.Thread(target=work, args=b) for b in bounds]
+    [t.start() for t in th]; [t.join() for t in th]
+    assert mismatches(out, want_v) == 0
+
+    def work2(lo, hi):
+        L.saxpy(y.ctypes.data + 4 * lo, x.ctypes.data + 4 * lo, 2.5, hi - lo, hi - lo)
+    th = [threading.Thread(target=work2, args=b) for b in bounds]
+    [t.start() for t in th]; [t.join() for t in th]
+    assert mismatches(y, want_s) == 0
+
+
 def test_full_size_saxpy_windows(sm, dev, oracle_lib):
     """N = 2^30 (4 GiB per vector): inputs generated in place on the device, the
     result checked bit for bit on windows at the start, an odd middle offset and
