@@ -826,6 +826,14 @@ __device__ __forceinline__ bool flag_wait_eq(const unsigned *flag, unsigned tag,
     }
 }
 
+// Makes this warp's partial sums visible and sets its hand-over word to the call's tag.
+__device__ __forceinline__ void publish_partial(unsigned *flag, unsigned tag, int lane)
+{
+    __threadfence();
+    __syncwarp();
+    if (lane == 0) asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flag), "r"(tag) : "memory");
+}
+
 constexpr int PARTIAL_FLOATS = 2 * 8 * 128 * 32;     // one cluster's slot: [cta][epilogue warp][4 columns][lane][4]
 
 }  // namespace gemm
@@ -955,6 +963,11 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
         uint32_t g = 0;
         WorkItem wi;
         bool ok = true;
+        // A partial handed over in the middle of the list is published one chunk later: its
+        // stores are issued at once, but waiting for them to land there and then (the fence
+        // before the release) held the drain up for 6 to 8 us beside the running loads, and
+        // the tensor pipe, two chunks ahead at most, stalled for 3 of them.
+        unsigned *unpublished = nullptr;
         while (ok && sched.next(wi)) {
 #pragma unroll
             for (int j = 0; j < HALF; j++) acc[j] = 0.0f;
@@ -975,6 +988,7 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) mbar_arrive_cluster(acc_empty_leader0 + 8 * buf);    // the leader counts both CTAs
+                if (unpublished) { publish_partial(unpublished, epoch, lane); unpublished = nullptr; }
             }
             if (!ok) break;
             int tm, tn;
@@ -988,12 +1002,9 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
 #pragma unroll
                 for (int j = 0; j < HALF / 4; j++)
                     dst[j * 32] = make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]);
-                __threadfence();
-                __syncwarp();
                 // one word per (cluster, CTA, epilogue warp), set to this call's tag: the owner's warp of
                 // the same role is the only reader of this warp's sums
-                if (lane == 0)
-                    asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(flags + cl * 16 + (int)rank * 8 + e), "r"(epoch) : "memory");
+                unpublished = flags + cl * 16 + (int)rank * 8 + e;
             } else {
                 if (wi.c1 != sched.nck) {
                     // owner of a shared tile: add the partials of the clusters that hold the rest of its K, always
@@ -1026,6 +1037,7 @@ gemm_tf32x3_persist(const __grid_constant__ CUtensorMap map_a_hi, const __grid_c
                 store_row<HALF>(c, acc, row, col0, M, N);
             }
         }
+        if (unpublished) publish_partial(unpublished, epoch, lane);      // the partial was this cluster's last work
         if (!__all_sync(0xffffffffu, ok)) {
             // A wait ran out: give copies that may still be in flight time to land
             // before the shared memory is released.
