@@ -216,6 +216,33 @@ d.close()
     assert len(lines) == 8 and all(ln.endswith("ok True") for ln in lines), res.stdout
 
 
+@pytest.mark.parametrize("sa,sb", [(1e-20, 1e15), (1e30, 1e5), (1.0, 1e-30), (1e-15, 1e-15)])
+def test_operand_scales_and_non_finite_values(sm, dev, sa, sb):
+    """The split into a TF32 value and a TF32 remainder must hold over fp32's range, not
+    only for U[-1,1): operands scaled far down and far up (products and remainders stay
+    normal numbers) keep the 1e-5 relative Frobenius bound against a float64 product. An
+    infinity in A turns the row of C it reaches into non-finite values (NaN: the remainder
+    of an infinity is inf - inf) and leaves every other row as it was."""
+    rng = np.random.default_rng(77)
+    M, N, K = 512, 512, 640
+    a = (rng.uniform(-1, 1, (M, K)) * sa).astype(np.float32)
+    b = (rng.uniform(-1, 1, (K, N)) * sb).astype(np.float32)
+    da, db, dc = dev.upload(a), dev.upload(b), dev.alloc(M * N * 4)
+    dev.gemm(dc, da, db, M, N, K); dev.sync()
+    c = dev.download(dc, (M, N), np.float32)
+    ref = a.astype(np.float64) @ b.astype(np.float64)
+    assert np.all(np.isfinite(c))
+    assert np.linalg.norm(c - ref) / np.linalg.norm(ref) <= 1e-5
+    a[7, 100] = np.inf
+    dev.h2d(da, a)
+    dev.gemm(dc, da, db, M, N, K); dev.sync()
+    c2 = dev.download(dc, (M, N), np.float32)
+    assert not np.any(np.isfinite(c2[7]))
+    keep = np.arange(M) != 7
+    assert np.array_equal(c2[keep], c[keep])
+    for p in (da, db, dc): dev.free(p)
+
+
 @pytest.mark.parametrize("pair", ["1", "0"])
 def test_barrier_wait_limit_reports_instead_of_hanging(sm, pair):
     """Failure detection without a fault: with the TMA producer kept silent (a
