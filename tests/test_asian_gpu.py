@@ -150,3 +150,32 @@ def test_same_bits_run_to_run(sm, dev, precise):
     first = gpu_sums(dev, prm, 12345, 300001)
     for _ in range(3):
         assert np.array_equal(gpu_sums(dev, prm, 12345, 300001).view(np.uint64), first.view(np.uint64))
+
+
+def test_pipe_probe_kernels_run_and_order_as_expected(sm, dev):
+    """The three probe kernels of the image (kernels/pipe_probe.cu) that bench.py times for the
+    pricer's second roofline: they load by name, run, leave their scratch word alone (they
+    write only on an impossible sum), and the two instruction groups together take longer
+    than either alone but less than one after the other."""
+    import ctypes as C
+    L = sm.lib()
+    scratch = dev.alloc(64)
+    dev.zero(scratch, 64)
+    ms = {}
+    for name in ("probe_mufu", "probe_imad_wide", "probe_mufu_imad_wide"):
+        k = sm.Kern()
+        assert L.sm100_rt_load_builtin(dev.handle, name.encode(), C.byref(k)) == 0
+        vals = [C.c_uint64(scratch), C.c_int(512), C.c_float(0.999), C.c_uint32(12345)]
+        argv = (C.c_void_p * len(vals))(*[C.cast(C.byref(v), C.c_void_p) for v in vals])
+        grid = dev.sm_count * 8
+        for _ in range(2):
+            assert L.sm100_rt_launch(dev.handle, C.byref(k), grid, 1, 1, 256, 1, 1, 0, argv) == 0
+        dev.sync(); dev.tic()
+        for _ in range(4):
+            assert L.sm100_rt_launch(dev.handle, C.byref(k), grid, 1, 1, 256, 1, 1, 0, argv) == 0
+        ms[name] = dev.toc() / 4
+        L.sm100_rt_unload(dev.handle, C.byref(k))
+    assert np.all(dev.download(scratch, 16, np.uint32) == 0)
+    both, a, b = ms["probe_mufu_imad_wide"], ms["probe_mufu"], ms["probe_imad_wide"]
+    assert both > 0.95 * max(a, b) and both < 1.05 * (a + b), ms
+    dev.free(scratch)
