@@ -37,13 +37,14 @@
 #include "common.cuh"
 
 // The 23 random bits as the mantissa of a float in [1, 2).
-__device__ __forceinline__ float mantissa_word(uint32_t x) { return __uint_as_float(0x3F800000u | (x >> 9)); }
+// One funnel shift, (0x7F : x) >> 9, is 0x3F800000 | (x >> 9). (Beside the scalar floating-point
+// code of the earlier version a shift and an OR were 2 % faster; beside the packed forms the single
+// instruction is, 4.89e9 against 4.80e9 paths/s, same bits.)
+__device__ __forceinline__ float mantissa_word(uint32_t x) { return __uint_as_float(__funnelshift_r(x, 0x7Fu, 9)); }
 
 __device__ __forceinline__ float u01(uint32_t x)
 {
-    // A shift and an OR, then one add. (One funnel shift, (0x7F : x) >> 9, gives the
-    // same bits in one instruction less, but measured 2 % slower: 4.54e9 against
-    // 4.62e9 paths/s.)
+    // The mantissa word minus (1 - 2^-24): exact.
     return __fadd_rn(mantissa_word(x), -0.99999994f);
 }
 
@@ -125,7 +126,7 @@ __device__ __forceinline__ Payoff asian_path(unsigned long long p, uint32_t k0, 
         // are kept as (even step, odd step) pairs and joined at the end. Besides the three
         // MUFU operations of a step, the ten rounds of a call are 20 IMAD.WIDE on the heavy
         // FMA pipe at a quarter of the FP32 rate; fewer FP32 instructions leave that pipe to
-        // them (4.79e9 against 4.60e9 paths per second). (vol below 1e-19, whose square
+        // them (4.79e9 against 4.60e9 paths per second; 4.89e9 with the funnel shift above). (vol below 1e-19, whose square
         // underflows, prices like vol = 0.)
         const float d2s = drift * 1.4426950f, v2 = vol * 1.4426950f;
         const float c_rv = (-2.0f * 0.6931472f) * (v2 * v2);            // -2 ln u * v2^2 = c_rv * log2 u
